@@ -5,8 +5,6 @@ S=gpurun_out/r2a_summary.txt; rm -f $S
 run() { local name=$1 t=$2; shift 2
   timeout -s KILL $t "$@" > gpurun_out/r2a_$name.out 2> gpurun_out/r2a_$name.err
   echo "$name exit=$?" >> $S; }
-B2L_HANG_MS=1500 run hang_legacy 120 python tools/hang_repro.py
-run hang_fixed 120 python tools/hang_repro.py --fixed
 run gemm_m1 60 python tools/qgemm_probe.py --m 1 --flags base,packed
 run stress 900 python -m pytest -q -p no:cacheprovider -x tests/test_stress_gpu.py -m gpu
 run tests 600 python -m pytest -q -p no:cacheprovider -x tests -m gpu --deselect tests/test_stress_gpu.py
