@@ -37,6 +37,7 @@ extern "C" {
 
 #define B2L_F16 0
 #define B2L_BF16 1
+#define B2L_F32 2 /* true 32-bit activations and weights: accepted by the entry points that say so */
 
 #define B2L_OK 0
 #define B2L_ERR_INVALID (-1)
@@ -249,6 +250,64 @@ int b2l_tp_comm_destroy(int64_t comm);
 int b2l_tp_allreduce_skip_rmsnorm(int64_t comm, void* y, const void* x_partial, void* residual, const void* weight,
                                   int64_t rows, int64_t n, int64_t x_row_stride, int64_t r_row_stride,
                                   int64_t y_row_stride, float eps, int dtype, void* stream);
+
+/* ---- layer-list models: fp32 residual stream, recurrent mixers, ragged steps -------------------------------------
+ * No reference counterpart (the reference serves rotary-attention decoders only).  Every entry point below accepts
+ * dtype B2L_F16 / B2L_BF16 / B2L_F32 for the activation AND weight element type; statistics, softmax, recurrent
+ * state and the residual stream are fp32 in all of them.  A ragged step is described by int32 device vectors:
+ * seq_start [num_seqs + 1] (token offsets into the flat batch), seq_ctx [num_seqs] (tokens the sequence already has
+ * in its cache / state), seq_slot [num_seqs] (its row of the request table and its recurrent-state slot). */
+
+/* y = x . w^T (+ bias) on the CUDA cores, fp32 accumulation in ascending k; any shape (csrc/gemm_simt.cu). */
+int b2l_gemm_simt(void* y, const void* x, const void* w, const void* bias, int64_t m, int64_t n, int64_t k,
+                  int64_t x_row_stride, int64_t w_row_stride, int64_t y_row_stride, int dtype, void* stream);
+
+/* residual[t] = embed[token[t]] + pos_table[pos[t]] (pos_table nullable); act (nullable) gets the copy in dtype. */
+int b2l_embed_positions(void* residual_f32, void* act, const void* tokens_i32, const void* pos_i32, const void* embed,
+                        const void* pos_table, int64_t rows, int64_t n, int64_t vocab, int64_t max_pos, int dtype,
+                        void* stream);
+/* residual += y / sqrt(mean(y^2) + eps) * (weight_offset + weight): the norm sits on the sublayer OUTPUT. */
+int b2l_post_norm_residual(void* residual_f32, void* act, const void* y, const void* weight, int64_t rows, int64_t n,
+                           int64_t y_row_stride, float eps, float weight_offset, int dtype, void* stream);
+/* out[i] = rmsnorm(residual[rows[i]]) * (weight_offset + weight); rows_i32 nullable = identity. */
+int b2l_rmsnorm_from_f32(void* out, const void* residual_f32, const void* rows_i32, const void* weight, int64_t rows,
+                         int64_t n, float eps, float weight_offset, int dtype, void* stream);
+int b2l_relu_squared(void* out, const void* x, int64_t total, int dtype, void* stream);
+
+/* Short causal convolution per channel + SiLU over a ragged step, and the slot's tail (last taps-1 inputs) update.
+ * in: [tokens, >= channels] with row stride; weight [channels, taps] (last column = current token); tail
+ * [slots, taps - 1, channels] in dtype. */
+int b2l_causal_conv_silu(void* out, const void* in, int64_t in_row_stride, const void* weight, const void* bias,
+                         void* tail, const void* seq_start, const void* seq_ctx, const void* seq_slot, int64_t num_seqs,
+                         int64_t tokens, int channels, int taps, int dtype, void* stream);
+/* Scalar-decay state-space recurrence (csrc/ssm_scan.cu).  xbc rows = [x: heads*head_dim | B: groups*state | C: ...];
+ * state_f32 [slots, heads, head_dim, state] fp32; y_f32 [tokens, heads*head_dim] fp32. */
+int b2l_ssm_scan(void* y_f32, void* state_f32, const void* xbc, int64_t xbc_row_stride, const void* dt_raw,
+                 int64_t dt_row_stride, const void* dt_bias, const void* a_log, const void* d_skip,
+                 const void* seq_start, const void* seq_ctx, const void* seq_slot, int64_t num_seqs, int heads,
+                 int groups, int state_size, int head_dim, int dtype, void* stream);
+/* out = unit_rms(y * silu(z)) * weight, the unit RMS taken in `groups` equal parts of the row. */
+int b2l_gated_group_norm(void* out, const void* y_f32, const void* z, int64_t z_row_stride, const void* weight,
+                         int64_t rows, int inner, int groups, float eps, int dtype, void* stream);
+
+/* Per token of a fused [q | k | v] projection: whole-row RMS norm of q and k with plain weights (nullable = none),
+ * query gain 1 + gain_coef * ln(floor((pos + 1) / gain_every) + 1) (gain_every <= 0: none), value mixing
+ * v <- (1 - lambda) v + lambda v_first_in (nullable), copy of the unmixed v to v_first_out (nullable), and the
+ * K|V write into pool row kv_rows[t].  q is updated in place. */
+int b2l_attn_prepare(void* qkv, int64_t qkv_row_stride, void* kv_pool, int64_t kv_row_stride, const void* kv_rows_i32,
+                     const void* pos_i32, const void* q_norm_weight, const void* k_norm_weight, const void* v_first_in,
+                     void* v_first_out, const void* v_lambda, int64_t tokens, int q_cols, int k_cols, int v_cols,
+                     float eps, float gain_coef, float gain_every, int dtype, void* stream);
+/* Soft-capped attention with an optional per-head sink over the pool (csrc/attention_sink.cu).  num_splits == 0: tiled
+ * mode for sequences of up to max_q_len new tokens; num_splits > 0: every listed sequence brings one token, its keys
+ * are cut into num_splits ranges of split_keys and merged (workspace: b2l_sink_attention_workspace_bytes). */
+int64_t b2l_sink_attention_workspace_bytes(int64_t num_seqs, int heads, int v_head_dim, int num_splits);
+int b2l_sink_attention(void* out, int64_t out_row_stride, const void* q, int64_t q_row_stride, const void* kv_pool,
+                       int64_t kv_row_stride, const void* table_i32, int64_t table_row_stride, const void* seq_start,
+                       const void* seq_ctx, const void* seq_slot, const void* seq_list, int64_t num_seqs,
+                       int max_q_len, const void* sink, int heads, int kv_heads, int head_dim, int v_head_dim,
+                       float scale, float softcap, int num_splits, int split_keys, void* workspace,
+                       int64_t workspace_bytes, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,325 @@
+// Attention over the token-granular KV pool for RAGGED steps, with the score shaping of the sink / soft-cap family:
+//   score = softcap * tanh(q.k * scale / softcap)   (softcap <= 0: plain q.k * scale)
+//   p_j   = exp(score_j) / (sum_i exp(score_i) + exp(sink_h))      (sink == NULL: ordinary softmax)
+// K and V rows may have different head sizes (D, Dv): a pool row is [G*D keys | G*Dv values].
+//
+//   attn_prepare   per token: whole-row RMS norm of q and of k (one statistic over ALL heads, plain weight),
+//                  position-dependent query gain, value mixing with an earlier layer's values, K|V cache write
+//   sink_attention sequence s brings q_len new tokens after ctx cached ones; token i sees cache positions 0..ctx+i
+//                  (its own K/V is already in the pool).  One launch covers a list of sequences:
+//                  * tiled mode: CTA = (token tile, kv head, sequence); the rows of a CTA (tokens x the kv head's
+//                    query heads) share every K/V tile that is staged in shared memory
+//                  * split mode (one new token per sequence: decode): CTA = (key range, kv head, sequence), fp32
+//                    partial (max, sum, acc) per range, merged with the sink by sink_attention_merge
+// Softmax statistics, scores and the output accumulator are fp32 whatever T is.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kRows = 16;      // query rows per CTA
+constexpr int kWarps = 4;
+constexpr int kRowsPerWarp = kRows / kWarps;
+constexpr int kKeys = 32;      // keys per tile: one per lane
+
+struct AttnArgs {
+  const void* q; int64_t q_stride;
+  const void* kv; int64_t kv_stride;
+  const int* table; int64_t table_stride;
+  const int* seq_start; const int* seq_ctx; const int* seq_slot; const int* seq_list;
+  const void* sink;
+  void* out; int64_t out_stride;
+  float* part;
+  int H, G, D, Dv, PH, BQ, nsplit, chunk;
+  float scale, softcap;
+};
+
+template <typename T, int DVJ, bool SPLIT>
+__global__ void __launch_bounds__(kWarps * 32) sink_attention_kernel(AttnArgs a) {
+  pdl_prologue();
+  extern __shared__ float smem[];
+  const int D = a.D, Dv = a.Dv, per = a.H / a.G;
+  float* qs = smem;                              // [kRows][D]
+  float* ks = qs + kRows * D;                    // [kKeys][D + 1]
+  float* vs = ks + kKeys * (D + 1);              // [kKeys][Dv]
+  const int z = blockIdx.z, s = a.seq_list ? a.seq_list[z] : z;
+  const int start = a.seq_start[s], qlen = a.seq_start[s + 1] - start, ctx = a.seq_ctx[s];
+  const int64_t slot = a.seq_slot[s];
+  const int hchunks = (per + a.PH - 1) / a.PH;
+  const int g = blockIdx.y / hchunks, h_first = g * per + (blockIdx.y % hchunks) * a.PH;
+  const int h_count = min(a.PH, g * per + per - h_first);
+  const int t0 = SPLIT ? 0 : blockIdx.x * a.BQ;
+  if (t0 >= qlen) return;
+  const int t_count = SPLIT ? 1 : min(a.BQ, qlen - t0);
+  const int key_lo = SPLIT ? blockIdx.x * a.chunk : 0;
+  const int key_hi = SPLIT ? min(key_lo + a.chunk, ctx + 1) : ctx + t0 + t_count;    // exclusive
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const T* q = (const T*)a.q;
+  const T* kv = (const T*)a.kv;
+  // rows: r = tl * PH + hl
+  for (int i = tid; i < kRows * D; i += blockDim.x) {
+    const int r = i / D, d = i - r * D, tl = r / a.PH, hl = r - tl * a.PH;
+    float v = 0.f;
+    if (tl < t_count && hl < h_count) v = to_f32(q[(int64_t)(start + t0 + tl) * a.q_stride + (h_first + hl) * D + d]);
+    qs[i] = v;
+  }
+  float m[kRowsPerWarp], l[kRowsPerWarp], acc[kRowsPerWarp][DVJ];
+  int row_pos[kRowsPerWarp];                      // last visible key position of the row, -1 = unused row
+#pragma unroll
+  for (int i = 0; i < kRowsPerWarp; ++i) {
+    const int r = warp * kRowsPerWarp + i, tl = r / a.PH, hl = r - tl * a.PH;
+    m[i] = -INFINITY; l[i] = 0.f;
+    row_pos[i] = (tl < t_count && hl < h_count) ? ctx + t0 + tl : -1;
+#pragma unroll
+    for (int j = 0; j < DVJ; ++j) acc[i][j] = 0.f;
+  }
+  const int* trow = a.table + slot * a.table_stride;
+  const float inv_cap = a.softcap > 0.f ? 1.0f / a.softcap : 0.f;
+  for (int k0 = key_lo; k0 < key_hi; k0 += kKeys) {
+    __syncthreads();
+    const int nk = min(kKeys, key_hi - k0);
+    for (int i = tid; i < kKeys * D; i += blockDim.x) {
+      const int j = i / D, d = i - j * D;
+      ks[j * (D + 1) + d] = j < nk ? to_f32(kv[(int64_t)trow[k0 + j] * a.kv_stride + g * D + d]) : 0.f;
+    }
+    for (int i = tid; i < kKeys * Dv; i += blockDim.x) {
+      const int j = i / Dv, d = i - j * Dv;
+      vs[i] = j < nk ? to_f32(kv[(int64_t)trow[k0 + j] * a.kv_stride + a.G * D + g * Dv + d]) : 0.f;
+    }
+    __syncthreads();
+    float sc[kRowsPerWarp];
+#pragma unroll
+    for (int i = 0; i < kRowsPerWarp; ++i) sc[i] = 0.f;
+    const float* kr = ks + lane * (D + 1);
+    const float* qr = qs + warp * kRowsPerWarp * D;
+    for (int d = 0; d < D; ++d) {
+      const float kvv = kr[d];
+#pragma unroll
+      for (int i = 0; i < kRowsPerWarp; ++i) sc[i] = fmaf(qr[i * D + d], kvv, sc[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < kRowsPerWarp; ++i) {
+      if (row_pos[i] < k0) continue;              // warp-uniform: nothing visible in this tile (or unused row)
+      float sv = sc[i] * a.scale;
+      if (a.softcap > 0.f) sv = a.softcap * tanhf(sv * inv_cap);
+      const bool ok = lane < nk && k0 + lane <= row_pos[i];
+      sv = ok ? sv : -INFINITY;
+      const float mt = warp_reduce_max(sv);
+      const float mn = fmaxf(m[i], mt);
+      const float corr = expf(m[i] - mn);          // exp(-inf) = 0 on the first tile
+      const float p = ok ? expf(sv - mn) : 0.f;
+      l[i] = l[i] * corr + warp_reduce_sum(p);
+      m[i] = mn;
+#pragma unroll
+      for (int j = 0; j < DVJ; ++j) acc[i][j] *= corr;
+      for (int kk = 0; kk < nk; ++kk) {
+        const float pk = __shfl_sync(0xffffffffu, p, kk);
+#pragma unroll
+        for (int j = 0; j < DVJ; ++j) {
+          const int d = lane + 32 * j;
+          if (d < Dv) acc[i][j] = fmaf(pk, vs[kk * Dv + d], acc[i][j]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kRowsPerWarp; ++i) {
+    if (row_pos[i] < 0) continue;
+    const int r = warp * kRowsPerWarp + i, tl = r / a.PH, hl = r - tl * a.PH, h = h_first + hl;
+    if (SPLIT) {
+      float* dst = a.part + (((int64_t)z * a.H + h) * a.nsplit + blockIdx.x) * (Dv + 2);
+      if (lane == 0) { dst[0] = m[i]; dst[1] = l[i]; }
+#pragma unroll
+      for (int j = 0; j < DVJ; ++j) {
+        const int d = lane + 32 * j;
+        if (d < Dv) dst[2 + d] = acc[i][j];
+      }
+    } else {
+      float mf = m[i], den = l[i], num = 1.f;
+      if (a.sink) {
+        const float sk = to_f32(((const T*)a.sink)[h]);
+        mf = fmaxf(m[i], sk);
+        num = expf(m[i] - mf);
+        den = l[i] * num + expf(sk - mf);
+      }
+      const float inv = num / den;
+      T* o = (T*)a.out + (int64_t)(start + t0 + tl) * a.out_stride + h * Dv;
+#pragma unroll
+      for (int j = 0; j < DVJ; ++j) {
+        const int d = lane + 32 * j;
+        if (d < Dv) o[d] = from_f32<T>(acc[i][j] * inv);
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void sink_attention_merge_kernel(T* __restrict__ out, int64_t out_stride, const float* __restrict__ part,
+                                            const T* __restrict__ sink, const int* __restrict__ seq_start,
+                                            const int* __restrict__ seq_list, int H, int Dv, int nsplit) {
+  pdl_prologue();
+  const int z = blockIdx.y, h = blockIdx.x, s = seq_list ? seq_list[z] : z;
+  const float* p = part + ((int64_t)z * H + h) * nsplit * (Dv + 2);
+  float mf = sink ? to_f32(sink[h]) : -INFINITY;
+  for (int i = 0; i < nsplit; ++i) mf = fmaxf(mf, p[i * (Dv + 2)]);
+  float den = sink ? expf(to_f32(sink[h]) - mf) : 0.f;
+  for (int i = 0; i < nsplit; ++i) den += p[i * (Dv + 2) + 1] * expf(p[i * (Dv + 2)] - mf);
+  T* o = out + (int64_t)seq_start[s] * out_stride + h * Dv;
+  for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
+    float v = 0.f;
+    for (int i = 0; i < nsplit; ++i) v = fmaf(p[i * (Dv + 2) + 2 + d], expf(p[i * (Dv + 2)] - mf), v);
+    o[d] = from_f32<T>(v / den);
+  }
+}
+
+__device__ __forceinline__ float block_sum2(float v, float* red) {
+  v = warp_reduce_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < nw ? red[lane] : 0.f;
+  t = warp_reduce_sum(t);
+  __syncthreads();
+  return t;
+}
+
+template <typename T>
+__global__ void attn_prepare_kernel(T* __restrict__ qkv, int64_t stride, T* __restrict__ kv, int64_t kv_stride,
+                                    const int* __restrict__ rows, const int* __restrict__ pos,
+                                    const T* __restrict__ qw, const T* __restrict__ kw, const T* __restrict__ v_first_in,
+                                    T* __restrict__ v_first_out, const T* __restrict__ lambda, int qn, int kn, int vn,
+                                    float eps, float gain_coef, double gain_every) {
+  pdl_prologue();
+  __shared__ float red[32];
+  const int64_t t = blockIdx.x;
+  T* q = qkv + t * stride;
+  T* k = q + qn;
+  T* v = k + kn;
+  T* dst = kv + (int64_t)rows[t] * kv_stride;
+  float gain = 1.f;
+  if (gain_every > 0.0) gain = 1.0f + gain_coef * logf((float)floor(((double)pos[t] + 1.0) / gain_every) + 1.0f);
+  if (qw) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < qn; i += blockDim.x) { const float x = to_f32(q[i]); ss = fmaf(x, x, ss); }
+    ss = block_sum2(ss, red);
+    const float rr = 1.0f / sqrtf(ss / (float)qn + eps);
+    for (int i = threadIdx.x; i < qn; i += blockDim.x) q[i] = from_f32<T>(to_f32(q[i]) * rr * to_f32(qw[i]) * gain);
+  } else if (gain != 1.f) {
+    for (int i = threadIdx.x; i < qn; i += blockDim.x) q[i] = from_f32<T>(to_f32(q[i]) * gain);
+  }
+  if (kw) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < kn; i += blockDim.x) { const float x = to_f32(k[i]); ss = fmaf(x, x, ss); }
+    ss = block_sum2(ss, red);
+    const float rr = 1.0f / sqrtf(ss / (float)kn + eps);
+    for (int i = threadIdx.x; i < kn; i += blockDim.x) dst[i] = from_f32<T>(to_f32(k[i]) * rr * to_f32(kw[i]));
+  } else {
+    for (int i = threadIdx.x; i < kn; i += blockDim.x) dst[i] = k[i];
+  }
+  const float lam = (v_first_in && lambda) ? to_f32(lambda[0]) : 0.f;
+  for (int i = threadIdx.x; i < vn; i += blockDim.x) {
+    const T raw = v[i];
+    if (v_first_out) v_first_out[t * vn + i] = raw;
+    T val = raw;
+    if (v_first_in) val = from_f32<T>((1.0f - lam) * to_f32(raw) + lam * to_f32(v_first_in[t * vn + i]));
+    dst[kn + i] = val;
+  }
+}
+
+template <typename T, bool SPLIT>
+int launch_attention(const AttnArgs& a, dim3 grid, cudaStream_t st) {
+  const size_t smem = (size_t)(kRows * a.D + kKeys * (a.D + 1) + kKeys * a.Dv) * sizeof(float);
+  B2L_REQUIRE((int64_t)smem <= b2l_max_smem_optin(), "sink_attention: head sizes %d / %d need %lld bytes of shared memory",
+              a.D, a.Dv, (long long)smem);
+  const int dvj = (a.Dv + 31) / 32;
+  B2L_REQUIRE(dvj <= 8, "sink_attention: value head size %d > 256", a.Dv);
+#define B2L_ATTN(J)                                                                                           \
+  do {                                                                                                        \
+    static int cache[64] = {0};                                                                               \
+    B2L_CUDA_CHECK(b2l_ensure_dynamic_smem(sink_attention_kernel<T, J, SPLIT>, (int)smem, cache));            \
+    b2l_launch(sink_attention_kernel<T, J, SPLIT>, grid, dim3(kWarps * 32), smem, st, a);                     \
+  } while (0)
+  if (dvj <= 2) B2L_ATTN(2);
+  else if (dvj <= 4) B2L_ATTN(4);
+  else B2L_ATTN(8);
+#undef B2L_ATTN
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}
+
+}  // namespace
+
+extern "C" int b2l_attn_prepare(void* qkv, int64_t qkv_row_stride, void* kv_pool, int64_t kv_row_stride,
+                                const void* kv_rows_i32, const void* pos_i32, const void* q_norm_weight,
+                                const void* k_norm_weight, const void* v_first_in, void* v_first_out,
+                                const void* v_lambda, int64_t tokens, int q_cols, int k_cols, int v_cols, float eps,
+                                float gain_coef, float gain_every, int dtype, void* stream) {
+  B2L_REQUIRE(qkv && kv_pool && kv_rows_i32 && pos_i32, "attn_prepare: null pointer");
+  B2L_REQUIRE(q_cols > 0 && k_cols > 0 && v_cols > 0, "attn_prepare: bad shape");
+  if (tokens <= 0) return B2L_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  B2L_DISPATCH_FLOAT(dtype, "attn_prepare", {
+    b2l_launch(attn_prepare_kernel<T>, dim3((unsigned)tokens), dim3(256), (size_t)0, st, (T*)qkv, qkv_row_stride,
+               (T*)kv_pool, kv_row_stride, (const int*)kv_rows_i32, (const int*)pos_i32, (const T*)q_norm_weight,
+               (const T*)k_norm_weight, (const T*)v_first_in, (T*)v_first_out, (const T*)v_lambda, q_cols, k_cols,
+               v_cols, eps, gain_coef, (double)gain_every);
+  });
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}
+
+extern "C" int64_t b2l_sink_attention_workspace_bytes(int64_t num_seqs, int heads, int v_head_dim, int num_splits) {
+  if (num_splits <= 0) return 0;
+  return num_seqs * heads * (int64_t)num_splits * (v_head_dim + 2) * 4;
+}
+
+/* num_splits == 0: tiled mode over `max_q_len`-token sequences; > 0: split mode, every listed sequence brings ONE token
+ * and `split_keys` keys go to each of the num_splits ranges (num_splits * split_keys >= longest context + 1). */
+extern "C" int b2l_sink_attention(void* out, int64_t out_row_stride, const void* q, int64_t q_row_stride,
+                                  const void* kv_pool, int64_t kv_row_stride, const void* table_i32,
+                                  int64_t table_row_stride, const void* seq_start, const void* seq_ctx,
+                                  const void* seq_slot, const void* seq_list, int64_t num_seqs, int max_q_len,
+                                  const void* sink, int heads, int kv_heads, int head_dim, int v_head_dim, float scale,
+                                  float softcap, int num_splits, int split_keys, void* workspace,
+                                  int64_t workspace_bytes, int dtype, void* stream) {
+  B2L_REQUIRE(out && q && kv_pool && table_i32 && seq_start && seq_ctx && seq_slot, "sink_attention: null pointer");
+  B2L_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "sink_attention: %d heads must be a multiple of num_kv_heads %d",
+              heads, kv_heads);
+  B2L_REQUIRE(head_dim > 0 && v_head_dim > 0 && max_q_len >= 1, "sink_attention: bad shape");
+  if (num_seqs <= 0) return B2L_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  AttnArgs a;
+  a.q = q; a.q_stride = q_row_stride; a.kv = kv_pool; a.kv_stride = kv_row_stride;
+  a.table = (const int*)table_i32; a.table_stride = table_row_stride;
+  a.seq_start = (const int*)seq_start; a.seq_ctx = (const int*)seq_ctx; a.seq_slot = (const int*)seq_slot;
+  a.seq_list = (const int*)seq_list; a.sink = sink; a.out = out; a.out_stride = out_row_stride;
+  a.part = (float*)workspace;
+  a.H = heads; a.G = kv_heads; a.D = head_dim; a.Dv = v_head_dim;
+  const int per = heads / kv_heads;
+  a.PH = per < kRows ? per : kRows;
+  a.BQ = kRows / a.PH;
+  a.nsplit = num_splits; a.chunk = split_keys; a.scale = scale; a.softcap = softcap;
+  const int hchunks = (per + a.PH - 1) / a.PH;
+  if (num_splits > 0) {
+    B2L_REQUIRE(split_keys > 0, "sink_attention: split_keys must be positive");
+    const int64_t need = b2l_sink_attention_workspace_bytes(num_seqs, heads, v_head_dim, num_splits);
+    B2L_REQUIRE(workspace && workspace_bytes >= need, "sink_attention: workspace too small (%lld < %lld)",
+                (long long)workspace_bytes, (long long)need);
+    a.BQ = 1;
+    a.PH = per < kRows ? per : kRows;
+    const dim3 grid((unsigned)num_splits, (unsigned)(kv_heads * hchunks), (unsigned)num_seqs);
+    int rc = B2L_OK;
+    B2L_DISPATCH_FLOAT(dtype, "sink_attention", { rc = launch_attention<T, true>(a, grid, st); });
+    if (rc != B2L_OK) return rc;
+    B2L_DISPATCH_FLOAT(dtype, "sink_attention", {
+      b2l_launch(sink_attention_merge_kernel<T>, dim3((unsigned)heads, (unsigned)num_seqs), dim3(64), (size_t)0, st,
+                 (T*)out, out_row_stride, (const float*)workspace, (const T*)sink, (const int*)seq_start,
+                 (const int*)seq_list, heads, v_head_dim, num_splits);
+    });
+    B2L_LAUNCH_CHECK();
+    return B2L_OK;
+  }
+  const dim3 grid((unsigned)((max_q_len + a.BQ - 1) / a.BQ), (unsigned)(kv_heads * hchunks), (unsigned)num_seqs);
+  int rc = B2L_OK;
+  B2L_DISPATCH_FLOAT(dtype, "sink_attention", { rc = launch_attention<T, false>(a, grid, st); });
+  return rc;
+}

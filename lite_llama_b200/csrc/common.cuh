@@ -62,6 +62,7 @@ void b2l_count_launch();
 // dtype enum shared with include/b200_lite_kernels.h
 #define B2L_F16 0
 #define B2L_BF16 1
+#define B2L_F32 2   // true 32-bit activations and weights (the layer-list models' exact mode)
 
 int b2l_pdl_enabled();        // programmatic dependent launch switch (b2l_set_pdl / env B2L_PDL; default on)
 int b2l_num_sms();            // cached cudaDevAttrMultiProcessorCount of the current device
@@ -80,7 +81,9 @@ template <> struct Vec2<__nv_bfloat16> { using type = __nv_bfloat162; };
 
 __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(float v) { return v; }
 template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
@@ -513,5 +516,14 @@ static inline cudaError_t b2l_launch(void (*kern)(KArgs...), dim3 grid, dim3 blo
   cfg.numAttrs = b2l_pdl_enabled() ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
+
+// Run `body` with `T` bound to the element type of dtype code `code` (host side, inside an int-returning function).
+#define B2L_DISPATCH_FLOAT(code, what, ...)                              \
+  do {                                                                   \
+    if ((code) == B2L_F16) { using T = __half; __VA_ARGS__ }             \
+    else if ((code) == B2L_BF16) { using T = __nv_bfloat16; __VA_ARGS__ } \
+    else if ((code) == B2L_F32) { using T = float; __VA_ARGS__ }         \
+    else B2L_UNSUPPORTED("%s: dtype %d", what, (int)(code));             \
+  } while (0)
 
 #endif  // __CUDACC__

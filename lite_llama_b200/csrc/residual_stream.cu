@@ -1,0 +1,139 @@
+// Kernels around an fp32 residual stream (layer-list models: the residual sum stays in 32 bits while the
+// projections run in the activation dtype T):
+//   * embed_positions      r = embed[token] + position_table[pos]                       (+ copy in T for the next GEMM)
+//   * post_norm_residual   r += y / sqrt(mean(y^2) + eps) * (offset + w)                (norm on the SUBLAYER OUTPUT)
+//   * rmsnorm_from_f32     o = r / sqrt(mean(r^2) + eps) * (offset + w), selected rows  (final norm before the head)
+//   * relu_squared         o = max(x, 0)^2
+// `offset` = 1 for weights stored around zero, 0 for plain weights.  All statistics in fp32.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_reduce_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.f;
+  t = warp_reduce_sum(t);
+  __syncthreads();
+  return t;
+}
+
+template <typename T>
+__global__ void embed_positions_kernel(float* __restrict__ r, T* __restrict__ act, const int* __restrict__ tokens,
+                                       const int* __restrict__ pos, const T* __restrict__ embed,
+                                       const T* __restrict__ ptab, int64_t n, int64_t vocab, int64_t max_pos) {
+  pdl_prologue();
+  const int64_t t = blockIdx.x;
+  int64_t tok = tokens[t], p = pos[t];
+  tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);        // ids are validated on the host; never read outside
+  const bool has_pos = ptab != nullptr;
+  p = p < 0 ? 0 : (p >= max_pos ? max_pos - 1 : p);
+  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = to_f32(embed[tok * n + i]);
+    if (has_pos) v += to_f32(ptab[p * n + i]);
+    r[t * n + i] = v;
+    if (act) act[t * n + i] = from_f32<T>(v);
+  }
+}
+
+template <typename T>
+__global__ void post_norm_residual_kernel(float* __restrict__ r, T* __restrict__ act, const T* __restrict__ y,
+                                          const T* __restrict__ w, int64_t n, int64_t ys, float eps, float offset) {
+  pdl_prologue();
+  __shared__ float red[32];
+  const int64_t t = blockIdx.x;
+  const T* yr = y + t * ys;
+  float ss = 0.f;
+  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) { const float v = to_f32(yr[i]); ss = fmaf(v, v, ss); }
+  ss = block_sum(ss, red);
+  const float rr = 1.0f / sqrtf(ss / (float)n + eps);
+  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = r[t * n + i] + to_f32(yr[i]) * rr * (offset + to_f32(w[i]));
+    r[t * n + i] = v;
+    if (act) act[t * n + i] = from_f32<T>(v);
+  }
+}
+
+template <typename T>
+__global__ void rmsnorm_from_f32_kernel(T* __restrict__ o, const float* __restrict__ r, const int* __restrict__ rows,
+                                        const T* __restrict__ w, int64_t n, float eps, float offset) {
+  pdl_prologue();
+  __shared__ float red[32];
+  const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
+  const float* x = r + src * n;
+  float ss = 0.f;
+  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(x[i], x[i], ss);
+  ss = block_sum(ss, red);
+  const float rr = 1.0f / sqrtf(ss / (float)n + eps);
+  for (int64_t i = threadIdx.x; i < n; i += blockDim.x)
+    o[(int64_t)blockIdx.x * n + i] = from_f32<T>(x[i] * rr * (offset + to_f32(w[i])));
+}
+
+template <typename T>
+__global__ void relu_squared_kernel(T* __restrict__ o, const T* __restrict__ x, int64_t total) {
+  pdl_prologue();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const float v = fmaxf(to_f32(x[i]), 0.f);
+    o[i] = from_f32<T>(v * v);
+  }
+}
+
+}  // namespace
+
+extern "C" int b2l_embed_positions(void* residual_f32, void* act, const void* tokens_i32, const void* pos_i32,
+                                   const void* embed, const void* pos_table, int64_t rows, int64_t n, int64_t vocab,
+                                   int64_t max_pos, int dtype, void* stream) {
+  B2L_REQUIRE(residual_f32 && tokens_i32 && pos_i32 && embed, "embed_positions: null pointer");
+  B2L_REQUIRE(rows >= 0 && n > 0 && vocab > 0, "embed_positions: bad shape");
+  if (rows == 0) return B2L_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  B2L_DISPATCH_FLOAT(dtype, "embed_positions", {
+    b2l_launch(embed_positions_kernel<T>, dim3((unsigned)rows), dim3(256), (size_t)0, st, (float*)residual_f32, (T*)act,
+               (const int*)tokens_i32, (const int*)pos_i32, (const T*)embed, (const T*)pos_table, n, vocab, max_pos);
+  });
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}
+
+extern "C" int b2l_post_norm_residual(void* residual_f32, void* act, const void* y, const void* weight, int64_t rows,
+                                      int64_t n, int64_t y_row_stride, float eps, float weight_offset, int dtype,
+                                      void* stream) {
+  B2L_REQUIRE(residual_f32 && y && weight, "post_norm_residual: null pointer");
+  B2L_REQUIRE(rows >= 0 && n > 0, "post_norm_residual: bad shape");
+  if (rows == 0) return B2L_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  B2L_DISPATCH_FLOAT(dtype, "post_norm_residual", {
+    b2l_launch(post_norm_residual_kernel<T>, dim3((unsigned)rows), dim3(256), (size_t)0, st, (float*)residual_f32,
+               (T*)act, (const T*)y, (const T*)weight, n, y_row_stride, eps, weight_offset);
+  });
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}
+
+extern "C" int b2l_rmsnorm_from_f32(void* out, const void* residual_f32, const void* rows_i32, const void* weight,
+                                    int64_t rows, int64_t n, float eps, float weight_offset, int dtype, void* stream) {
+  B2L_REQUIRE(out && residual_f32 && weight, "rmsnorm_from_f32: null pointer");
+  B2L_REQUIRE(rows >= 0 && n > 0, "rmsnorm_from_f32: bad shape");
+  if (rows == 0) return B2L_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  B2L_DISPATCH_FLOAT(dtype, "rmsnorm_from_f32", {
+    b2l_launch(rmsnorm_from_f32_kernel<T>, dim3((unsigned)rows), dim3(256), (size_t)0, st, (T*)out,
+               (const float*)residual_f32, (const int*)rows_i32, (const T*)weight, n, eps, weight_offset);
+  });
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}
+
+extern "C" int b2l_relu_squared(void* out, const void* x, int64_t total, int dtype, void* stream) {
+  B2L_REQUIRE(out && x, "relu_squared: null pointer");
+  if (total <= 0) return B2L_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const unsigned grid = (unsigned)(cdiv64(total, 256) < 148 * 16 ? cdiv64(total, 256) : 148 * 16);
+  B2L_DISPATCH_FLOAT(dtype, "relu_squared", {
+    b2l_launch(relu_squared_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (T*)out, (const T*)x, total);
+  });
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}

@@ -3,7 +3,10 @@ attention metadata, the KV pool + bump allocator, and the ModelRunner that drive
 
 from .attention_metadata import AttentionMetadata
 from .kv_cache_manager import KVCacheManager
-from .model_config import ModelConfig, PRESETS
-from .model_runner import ModelRunner
+from .model_config import DenseMlpSpec, LayeredConfig, LayerSpec, Mamba2Spec, ModelConfig, PRESETS, SinkAttentionSpec
+from .model_runner import ModelRunner, RequestState
+from .ragged_batch import RaggedBatch
+from .state_manager import RecurrentStateManager
 
-__all__ = ["AttentionMetadata", "KVCacheManager", "ModelConfig", "PRESETS", "ModelRunner"]
+__all__ = ["AttentionMetadata", "KVCacheManager", "ModelConfig", "PRESETS", "ModelRunner", "RequestState", "RaggedBatch",
+           "RecurrentStateManager", "LayeredConfig", "LayerSpec", "Mamba2Spec", "SinkAttentionSpec", "DenseMlpSpec"]

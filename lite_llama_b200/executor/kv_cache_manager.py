@@ -21,7 +21,11 @@ import torch
 
 class KVCacheManager:
     def __init__(self, num_layers: int, num_kv_heads: int, head_dim: int, gpu_num_blocks: int,
-                 block_size: int = 1, dtype: torch.dtype = torch.float16, device: str = "cuda") -> None:
+                 block_size: int = 1, dtype: torch.dtype = torch.float16, device: str = "cuda",
+                 row_widths: list[int] | None = None) -> None:
+        """``row_widths``: one entry per cached layer = elements of one token's row (all K heads, then all V heads);
+        for models whose layers differ, or whose K and V head sizes differ, the pool of such a layer is the 2-D
+        ``[max_tokens, width]`` instead of ``[max_tokens, 2 * num_kv_heads, head_dim]``."""
         if block_size != 1:
             raise ValueError("token attention uses block_size == 1")
         self.num_layers = num_layers
@@ -38,10 +42,15 @@ class KVCacheManager:
         self.kv_mem_use_state = torch.zeros(self.max_num_tokens, dtype=torch.int32, device=device)
         self._bump_cursor = 0
         self._bump_is_exact = True
-        self.gpu_kv_buffer = [
-            torch.empty((self.max_num_tokens, 2 * num_kv_heads, head_dim), dtype=dtype, device=device)
-            for _ in range(num_layers)
-        ]
+        if row_widths is not None:
+            if len(row_widths) != num_layers:
+                raise ValueError("row_widths needs one entry per cached layer")
+            self.gpu_kv_buffer = [torch.empty((self.max_num_tokens, w), dtype=dtype, device=device) for w in row_widths]
+        else:
+            self.gpu_kv_buffer = [
+                torch.empty((self.max_num_tokens, 2 * num_kv_heads, head_dim), dtype=dtype, device=device)
+                for _ in range(num_layers)
+            ]
 
     # ------------------------------------------------------------ allocation #
     def _free_rows(self) -> torch.Tensor:

@@ -68,3 +68,98 @@ PRESETS: dict[str, ModelConfig] = {
     "tiny-qwen2": ModelConfig("tiny-qwen2", 256, 2, 8, 2, 32, 512, 1000, rope_theta=1e4, qkv_bias=True,
                               rms_norm_eps=1e-6),
 }
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Layer-list models: every layer names its own mixer (attention or a recurrent one) and feed-forward, so the
+# geometry is a tuple of layer specs instead of one set of sizes.  The reference has no such family (its configs
+# are uniform decoders, lite_llama/models/config.py:48-218); the specs below are what the executor asks about one.
+# ---------------------------------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class Mamba2Spec:
+    """Scalar-decay state-space mixer: ``heads`` heads of ``head_dim`` channels, ``state`` rows of state per head,
+    B / C shared by ``groups`` groups of heads, output norm in ``norm_groups`` parts, ``conv`` convolution taps."""
+
+    heads: int
+    head_dim: int
+    state: int
+    groups: int = 1
+    norm_groups: int = 1
+    conv: int = 4
+
+    @property
+    def inner(self) -> int:
+        return self.heads * self.head_dim
+
+    @property
+    def conv_channels(self) -> int:
+        return self.inner + 2 * self.groups * self.state
+
+    @property
+    def in_rows(self) -> int:                       # [z | x | B | C | dt]
+        return 2 * self.inner + 2 * self.groups * self.state + self.heads
+
+    def validate(self) -> None:
+        if self.heads % self.groups or self.inner % self.norm_groups or self.conv < 1 or self.state > 256:
+            raise ValueError(f"unsupported state-space mixer geometry: {self}")
+
+
+@dataclass(frozen=True)
+class SinkAttentionSpec:
+    """Position-free attention: whole-row q / k norms, a query gain that grows with the logarithm of the position
+    (``1 + gain_coef * ln(floor((p + 1) / gain_every) + 1)``; ``gain_every == 0``: none), ``tanh`` soft cap
+    (0: none), a learned per-head sink in the softmax denominator, value mixing across the layers that ask for it."""
+
+    heads: int
+    kv_heads: int
+    head_dim: int
+    v_head_dim: int
+    scale: float
+    softcap: float = 0.0
+    gain_coef: float = 0.0
+    gain_every: float = 0.0
+    v_mix: bool = False
+
+    def validate(self) -> None:
+        if self.heads % self.kv_heads or self.v_head_dim > 256:
+            raise ValueError(f"unsupported attention geometry: {self}")
+
+
+@dataclass(frozen=True)
+class DenseMlpSpec:
+    ff: int
+    activation: str = "relu2"
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    kind: str                                          # key of executor.layered_decoder.MIXERS
+    mixer: Mamba2Spec | SinkAttentionSpec
+    mlp: DenseMlpSpec | None = None
+
+
+@dataclass(frozen=True)
+class LayeredConfig:
+    name: str
+    hidden_size: int
+    vocab_size: int
+    max_seq_len: int                                   # learned position table length
+    rms_norm_eps: float
+    layers: tuple[LayerSpec, ...] = ()
+
+    @property
+    def num_layers(self) -> int:
+        return len(self.layers)
+
+    def attention_layers(self) -> list[int]:
+        return [i for i, l in enumerate(self.layers) if isinstance(l.mixer, SinkAttentionSpec)]
+
+    def recurrent_layers(self) -> list[int]:
+        return [i for i, l in enumerate(self.layers) if isinstance(l.mixer, Mamba2Spec)]
+
+    def validate(self) -> None:
+        for l in self.layers:
+            l.mixer.validate()
+
+    def with_(self, **kw) -> "LayeredConfig":
+        return replace(self, **kw)

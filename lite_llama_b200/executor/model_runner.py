@@ -25,8 +25,10 @@ from ..kernels._common import counters
 from .attention_metadata import AttentionMetadata
 from .decoder import Decoder, DecoderWeights, random_weights
 from .kv_cache_manager import KVCacheManager
-from .model_config import PRESETS, ModelConfig
+from .model_config import PRESETS, LayeredConfig, ModelConfig
+from .ragged_batch import RaggedBatch
 from .slot_batch import SlotBatch
+from .state_manager import RecurrentStateManager
 
 # executor/cuda_graph.py:27 stops at 128; 256 added so that a 256-wide continuous batch (BASELINE configs[3]) stays
 # on the graph path
@@ -183,12 +185,32 @@ class GreedyDecodeLoop:
         self.graph.replay()
 
 
+class RequestState:
+    """What the runner keeps per live request of a ragged-step model: its slot (row of the request table and
+    recurrent-state slot), how many tokens it has in the cache / state, and the pool rows it holds."""
+
+    __slots__ = ("slot", "num_cached", "rows")
+
+    def __init__(self, slot: int) -> None:
+        self.slot = slot
+        self.num_cached = 0
+        self.rows: list[torch.Tensor] = []
+
+
 class ModelRunner:
-    def __init__(self, config: ModelConfig, weights: DecoderWeights, max_gpu_num_blocks: int,
-                 device: str = "cuda", dtype: torch.dtype = torch.float16) -> None:
+    def __init__(self, config: ModelConfig | LayeredConfig, weights, max_gpu_num_blocks: int,
+                 device: str = "cuda", dtype: torch.dtype = torch.float16, max_requests: int | None = None) -> None:
         self.config = config
         self.device = device
         self.dtype = dtype
+        self.ragged_steps = isinstance(config, LayeredConfig)
+        self._slot_batch: SlotBatch | None = None
+        self._graphs: dict[tuple[int, int], _CapturedDecode] = {}
+        self._graph_batches: tuple[int, ...] = ()
+        self._graph_buckets: tuple[int, ...] = ()
+        if self.ragged_steps:
+            self._init_layered(config, weights, max_gpu_num_blocks, max_requests or 4)
+            return
         self.num_layers = config.num_layers
         self.num_kv_heads = divide(config.num_kv_heads, get_tp_world_size(), "key/value heads")
         self.head_dim = config.head_dim
@@ -206,11 +228,104 @@ class ModelRunner:
         self.atten_info.b_req_tokens_table = self.b_req_tokens_table
         self.model = Decoder(config, weights, max_pos=self.max_seq_len, device=device, dtype=dtype)
         self.spec = ModelSpec(config.name)
-        self._slot_batch: SlotBatch | None = None
-        self._graphs: dict[tuple[int, int], _CapturedDecode] = {}
-        self._graph_batches: tuple[int, ...] = ()
-        self._graph_buckets: tuple[int, ...] = ()
         counters(torch.device(device))  # allocate the split-K ticket buffer outside any capture
+
+    # ------------------------------------------------------- layer-list models #
+    def _init_layered(self, config: LayeredConfig, weights, max_tokens: int, max_requests: int) -> None:
+        """Pool of ``max_tokens`` rows shared by all requests (one 2-D buffer per attention layer: layers may differ
+        in head count and K / V head size), ``max_requests`` slots of recurrent state, one request -> rows table."""
+        from .layered_decoder import LayeredDecoder
+
+        self.num_layers = config.num_layers
+        self.vocab_size = config.vocab_size
+        self.max_seq_len = config.max_seq_len
+        self.max_request_num = max_requests
+        attn = config.attention_layers()
+        widths = [config.layers[i].mixer.kv_heads * (config.layers[i].mixer.head_dim + config.layers[i].mixer.v_head_dim)
+                  for i in attn]
+        self.kv_cache_manager = KVCacheManager(len(attn), 0, 0, max_tokens, dtype=self.dtype, device=self.device,
+                                               row_widths=widths)
+        self.kv_buffer_of = dict(zip(attn, self.kv_cache_manager.gpu_kv_buffer))
+        self.state_manager = RecurrentStateManager(config, max_requests, self.dtype, self.device)
+        self.b_req_tokens_table = torch.zeros((max_requests, self.max_seq_len), dtype=torch.int32, device=self.device)
+        self.atten_info = AttentionMetadata(kv_buffer=self.kv_cache_manager.gpu_kv_buffer,
+                                            b_req_tokens_table=self.b_req_tokens_table)
+        self.model = LayeredDecoder(config, weights, device=self.device, dtype=self.dtype)
+        self.spec = ModelSpec(config.name)
+
+    @classmethod
+    def from_checkpoint(cls, model_dir, dtype: torch.dtype = torch.bfloat16, max_tokens: int = 4096,
+                        max_requests: int = 4, device: str = "cuda") -> "ModelRunner":
+        """Model class, configuration and weights from a checkpoint directory (``config.json`` + ``*.safetensors``);
+        the architecture registry decides which decoder serves it (reference: ModelRunner._load_model,
+        lite_llama/executor/model_runner.py:92-133)."""
+        from .checkpoint import read_checkpoint
+        from .registry import read_config
+
+        arch, cfg = read_config(model_dir)
+        weights = arch.map_weights(cfg, read_checkpoint(model_dir), device, dtype)
+        return cls(cfg, weights, max_tokens, device=device, dtype=dtype, max_requests=max_requests)
+
+    def open_request(self) -> RequestState:
+        return RequestState(self.state_manager.acquire())
+
+    def close_request(self, req: RequestState) -> None:
+        """Give the request's pool rows and its slot back."""
+        if req.rows:
+            self.kv_cache_manager.release_ref(torch.cat(req.rows))
+            req.rows = []
+        self.state_manager.release(req.slot)
+        req.num_cached = 0
+
+    def rows_needed(self, tokens: int) -> int:
+        return tokens
+
+    @torch.no_grad()
+    def forward_ragged(self, entries: list[tuple[RequestState, list[int]]],
+                       want: list[int] | None = None) -> torch.Tensor:
+        """One step over a flat batch: ``entries[i] = (request, its next tokens)``; ``want`` = flat indices of the
+        tokens whose logits are returned (default: the last token of every entry).  Allocates the step's pool
+        rows, extends the request table, runs the decoder, and advances every request's cached length."""
+        lens = [len(t) for _, t in entries]
+        if not entries or min(lens) < 1:
+            raise ValueError("forward_ragged: every entry brings at least one token")
+        total = sum(lens)
+        ctxs = [r.num_cached for r, _ in entries]
+        slots = [r.slot for r, _ in entries]
+        if len(set(slots)) != len(slots):
+            raise ValueError("forward_ragged: a request appears twice in one step")
+        for c, n in zip(ctxs, lens):
+            if c + n > self.max_seq_len:
+                raise ValueError(f"sequence of {c + n} tokens exceeds max_seq_len {self.max_seq_len}")
+        rows = self.kv_cache_manager.alloc_kvcache(total)
+        if rows is None:
+            raise RuntimeError(f"KV pool exhausted: {total} rows wanted, {self.kv_cache_manager.can_use_mem_size} free")
+        flat_ids: list[int] = []
+        table_idx: list[int] = []
+        at = 0
+        for (req, toks), n, c in zip(entries, lens, ctxs):
+            flat_ids.extend(toks)
+            table_idx.extend(range(req.slot * self.max_seq_len + c, req.slot * self.max_seq_len + c + n))
+            req.rows.append(rows[at:at + n])
+            at += n
+        if min(flat_ids) < 0 or max(flat_ids) >= self.vocab_size:
+            raise ValueError("token id outside the vocabulary")
+        if want is None:
+            want, at = [], 0
+            for n in lens:
+                at += n
+                want.append(at - 1)
+        host = torch.tensor(flat_ids + table_idx + list(want), dtype=torch.int32)
+        dev = (host.pin_memory() if torch.cuda.is_available() else host).to(self.device, non_blocking=True)
+        ids, tidx, want_rows = dev[:total], dev[total:2 * total], dev[2 * total:]
+        rows32 = rows.to(torch.int32)
+        self.b_req_tokens_table.view(-1).index_copy_(0, tidx.long(), rows32)
+        batch = RaggedBatch.build(lens, ctxs, slots, rows32, self.device)
+        logits = self.model.forward(ids, batch, self.kv_buffer_of, self.b_req_tokens_table, self.state_manager,
+                                    want_rows)
+        for (req, _), n in zip(entries, lens):
+            req.num_cached += n
+        return logits
 
     # ------------------------------------------------------------------ build #
     @classmethod

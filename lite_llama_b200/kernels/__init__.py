@@ -8,7 +8,10 @@ hand-written sm_100a CUDA from ``libb200lite.so`` on the current CUDA stream.
 from .flashattention2_nopad import flash_attention2_no_pad
 from .flashdecoding import flash_decoding
 from .fused_moe import fused_moe, moe_align_block_size, route_topk
-from .linear import linear
+from .linear import linear, linear_simt
+from .residual_stream import embed_positions, post_norm_residual, relu_squared, rmsnorm_from_f32
+from .sink_attention import attn_prepare, sink_attention
+from .ssm import causal_conv_silu, gated_group_norm, ssm_scan
 from .rope_emb import rope_emb_forward, rope_emb_inplace, rope_kv_write
 from .sampling import argmax_rows
 from .skip_rmsnorm import can_fuse_int8_quant, skip_rmsnorm, skip_rmsnorm_quant_int8
@@ -24,6 +27,16 @@ __all__ = [
     "moe_align_block_size",
     "route_topk",
     "linear",
+    "linear_simt",
+    "embed_positions",
+    "post_norm_residual",
+    "rmsnorm_from_f32",
+    "relu_squared",
+    "attn_prepare",
+    "sink_attention",
+    "causal_conv_silu",
+    "ssm_scan",
+    "gated_group_norm",
     "argmax_rows",
     "rope_emb_forward",
     "rope_emb_inplace",

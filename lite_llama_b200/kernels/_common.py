@@ -6,9 +6,10 @@ import torch
 
 from .. import _lib
 
-F16, BF16 = 0, 1
+F16, BF16, F32 = 0, 1, 2
 
 _DTYPE_CODE = {torch.float16: F16, torch.bfloat16: BF16}
+_FLOAT_CODE = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32}
 
 
 def lib():
@@ -24,6 +25,14 @@ def dtype_code(t: torch.Tensor, what: str) -> int:
         return _DTYPE_CODE[t.dtype]
     except KeyError:
         raise ValueError(f"{what} must be float16 or bfloat16, got {t.dtype}") from None
+
+
+def float_code(t: torch.Tensor, what: str) -> int:
+    """Dtype code for the entry points that also run in true 32-bit."""
+    try:
+        return _FLOAT_CODE[t.dtype]
+    except KeyError:
+        raise ValueError(f"{what} must be float16, bfloat16 or float32, got {t.dtype}") from None
 
 
 def require_cuda(*tensors: torch.Tensor) -> None:
