@@ -872,6 +872,9 @@ extern "C" int b2l_argmax_rows(void* out_index_i64, const void* x, int64_t rows,
   else if (dtype == B2L_BF16)
     b2l_launch(argmax_rows_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(threads), (size_t)0, st,
                (int64_t*)out_index_i64, (const __nv_bfloat16*)x, n, row_stride, vec);
+  else if (dtype == B2L_F32)   // the 8-element vector path is sized for 16-bit values: scalar loads
+    b2l_launch(argmax_rows_kernel<float>, dim3((unsigned)rows), dim3(threads), (size_t)0, st, (int64_t*)out_index_i64,
+               (const float*)x, n, row_stride, 0);
   else
     B2L_UNSUPPORTED("argmax_rows: dtype %d", dtype);
   B2L_LAUNCH_CHECK();

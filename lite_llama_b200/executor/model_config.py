@@ -160,6 +160,10 @@ class LayeredConfig:
     def validate(self) -> None:
         for l in self.layers:
             l.mixer.validate()
+        shared = {l.mixer.kv_heads * l.mixer.v_head_dim for l in self.layers
+                  if isinstance(l.mixer, SinkAttentionSpec) and l.mixer.v_mix}
+        if len(shared) > 1:
+            raise ValueError(f"value-mixing layers must agree on the width of their values, got {sorted(shared)}")
 
     def with_(self, **kw) -> "LayeredConfig":
         return replace(self, **kw)

@@ -39,7 +39,7 @@ def lookup(name: str) -> Architecture:
 
 def names() -> list[str]:
     _ensure_builtin()
-    return sorted(_REGISTRY)
+    return sorted(a.name for a in _REGISTRY.values())
 
 
 def read_config(model_dir: str | Path) -> tuple[Architecture, Any]:

@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import torch
 
-from ._common import check, dtype_code, lib, require_cuda, stream_handle
+from ._common import check, float_code, lib, require_cuda, stream_handle
 
 
 @torch.no_grad()
@@ -20,5 +20,5 @@ def argmax_rows(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.
     elif out.dtype != torch.int64 or out.numel() != rows or not out.is_contiguous():
         raise ValueError("argmax_rows: out must be a contiguous int64 tensor with one entry per row")
     check(lib().b2l_argmax_rows(out.data_ptr(), logits.data_ptr(), rows, n, logits.stride(0),
-                                dtype_code(logits, "logits"), stream_handle()))
+                                float_code(logits, "logits"), stream_handle()))
     return out
