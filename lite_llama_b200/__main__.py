@@ -39,11 +39,12 @@ def main(argv: list[str] | None = None) -> int:
 
         print("\n".join(registry.names()))
         return 0
-    from .build import build
+    from .build import LAYERED_SOURCES, build
 
-    build(verbose=a.cmd == "build")
     if a.cmd == "build":
+        build(verbose=True)
         return 0
+    build(verbose=False, sources=LAYERED_SOURCES)      # checkpoint directories hold layer-list models
     if a.cmd == "trace":
         from .trace import replay
 

@@ -64,15 +64,28 @@ def load() -> ctypes.CDLL:
             "`python -m lite_llama_b200.build` (nvcc, sm_100a)."
         )
     lib = ctypes.CDLL(str(LIB_PATH))
+    from .build import CSRC, linked_sources
+
+    partial = bool(linked_sources()) and linked_sources() != {p.stem for p in CSRC.glob("*.cu")}
     for name, (ret, args) in parse_header().items():
         try:
             fn = getattr(lib, name)
         except AttributeError as e:  # header declares a symbol the library does not export
+            if partial:              # a subset build (build(sources=...)): the symbol fails when it is CALLED
+                setattr(lib, name, _missing(name))
+                continue
             raise LibraryMissing(f"{LIB_PATH.name} does not export {name}; rebuild the library") from e
         fn.restype = _CTYPES[ret]
         fn.argtypes = [_CTYPES[a] for a in args]
     _lib = lib
     return lib
+
+
+def _missing(name: str):
+    def raiser(*_a, **_k):
+        raise LibraryMissing(f"{LIB_PATH.name} was built from a subset of the sources and has no {name}; run "
+                             "`python -m lite_llama_b200.build` for the full library")
+    return raiser
 
 
 def _fnv1a(name: str) -> int:

@@ -7,6 +7,10 @@ library only depends on the (statically linked) CUDA runtime.
 Usage:
     python -m lite_llama_b200.build            # incremental
     python -m lite_llama_b200.build --force
+
+``build(sources=...)`` compiles and links only the named sources (plus the library plumbing): a first run that
+serves one model family does not wait for the kernels of the others.  A library that already holds the wanted
+sources (a fuller build) is left alone; a later full build relinks.
 """
 
 from __future__ import annotations
@@ -59,20 +63,43 @@ def _compile(src: Path, force: bool) -> Path:
     return obj
 
 
-def build(force: bool = False, verbose: bool = True) -> Path:
+# plumbing every subset needs (error strings, launch counter, TMA descriptors)
+BASE_SOURCES = ("core", "tma_desc")
+# what the layer-list decoders launch: dense tcgen05 GEMM, fp32 / odd-shape GEMM, residual stream, state-space and
+# sink-attention kernels, argmax
+LAYERED_SOURCES = ("gemm_dense", "gemm_simt", "residual_stream", "ssm_scan", "attention_sink", "elementwise")
+LINK_STAMP = OBJ_DIR / "link.stamp"
+
+
+def linked_sources() -> set[str]:
+    """Source stems the current library was linked from (empty when there is none)."""
+    if not OUT.exists() or not LINK_STAMP.exists():
+        return set()
+    return set(LINK_STAMP.read_text().split())
+
+
+def build(force: bool = False, verbose: bool = True, sources: tuple[str, ...] | None = None) -> Path:
     OBJ_DIR.mkdir(exist_ok=True)
-    sources = sorted(CSRC.glob("*.cu"))
-    if not sources:
+    every = sorted(CSRC.glob("*.cu"))
+    if not every:
         raise RuntimeError(f"no CUDA sources under {CSRC}")
-    with ThreadPoolExecutor(max_workers=min(8, len(sources))) as pool:
-        objs = list(pool.map(lambda s: _compile(s, force), sources))
+    if sources is not None:
+        wanted = set(BASE_SOURCES) | set(sources)
+        have = linked_sources()
+        if wanted <= have and not force:
+            wanted = have                     # a fuller library is kept (and refreshed if its sources changed)
+        every = [s for s in every if s.stem in wanted]
+    with ThreadPoolExecutor(max_workers=min(8, len(every))) as pool:
+        objs = list(pool.map(lambda s: _compile(s, force), every))
     newest = max(o.stat().st_mtime for o in objs)
-    if force or not OUT.exists() or OUT.stat().st_mtime < newest:
+    stems = sorted(s.stem for s in every)
+    if force or not OUT.exists() or OUT.stat().st_mtime < newest or linked_sources() != set(stems):
         cmd = [_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC",
                "-o", str(OUT), *map(str, objs)]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+        LINK_STAMP.write_text(" ".join(stems))
         if verbose:
             print(f"[b200lite] linked {OUT} from {len(objs)} objects")
     elif verbose:
