@@ -40,6 +40,10 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--design", default=None, choices=["gufotar"],
+                    help="instead of the headline workload: prefill / decode throughput and per-kernel rooflines of a "
+                         "layer-list design beside the closest uniform decoder (bench_design.py); 1 GPU")
+    ap.add_argument("--design-sizes", default=None, help="comma-separated subset of bench_design.SIZES")
     ap.add_argument("--model", default="llama-3-8b")
     ap.add_argument("--quant", default="int4", choices=["fp16", "int4", "int8", "fp8", "smoothquant"])
     ap.add_argument("--max-seq-len", type=int, default=None, help="KV slot length per request (default: fits the run)")
@@ -317,6 +321,11 @@ def main() -> None:
         arm_watchdog(args.watchdog_s)
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.design:
+        import bench_design
+
+        bench_design.run(args)
         return
 
     import torch.distributed as dist

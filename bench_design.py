@@ -1,0 +1,274 @@
+"""``bench.py --design gufotar``: prefill and decode throughput of the layer-list design at a few sizes that resemble
+a real model's layers (random weights, synthetic ids), beside the closest existing model of the framework (the
+uniform rotary decoder: same width, layer count, attention geometry and feed-forward width), plus every kernel of the
+new path timed alone against its like kernel with the fraction of the measured roofline each reaches.
+
+Timing: CUDA events on the launching stream, >= 3 warm-up runs, a 256 MiB write between timed runs (larger than the
+126 MB L2), median of the timed runs.  Step figures include the host work of a step (metadata build, allocation).
+"""
+
+from __future__ import annotations
+
+import json
+import math
+import statistics
+import time
+
+import torch
+
+SIZES = {
+    # name: width, layers, heads, kv_heads, head_dim, ff, vocab | state-space: heads, head_dim, state, groups
+    "1b": dict(width=2048, layers=8, heads=16, kv_heads=4, head_dim=128, ff=8192, vocab=32000,
+               s_heads=64, s_dim=64, s_state=128, s_groups=8),
+    "8b": dict(width=4096, layers=8, heads=32, kv_heads=8, head_dim=128, ff=14336, vocab=32000,
+               s_heads=128, s_dim=64, s_state=128, s_groups=8),
+    "small": dict(width=1024, layers=4, heads=16, kv_heads=4, head_dim=64, ff=4096, vocab=32000,
+                  s_heads=32, s_dim=64, s_state=64, s_groups=4),
+}
+
+
+def _flush_buffer(dev):
+    return torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+
+def timed(fn, flush, warmup=3, reps=7) -> float:
+    """Median device milliseconds of ``fn()``."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    return statistics.median(ts)
+
+
+def gufotar_config(sz: dict, max_positions: int) -> dict:
+    layers = []
+    for i in range(sz["layers"]):
+        if i % 2 == 0:
+            layers.append({"type": "mamba2", "mlp": None,
+                           "mixer": {"conv": 4, "groups": sz["s_groups"], "heads": sz["s_heads"], "norm_groups": sz["s_groups"],
+                                     "state": sz["s_state"], "vdim": sz["s_dim"]}})
+        else:
+            layers.append({"type": "attention", "mlp": {"ff": sz["ff"], "kind": "dense"},
+                           "mixer": {"dim": sz["head_dim"], "heads": sz["heads"], "kv_heads": sz["kv_heads"],
+                                     "q_temp": {"coef": 0.5, "every": 64}, "scale": 1.0 / math.sqrt(sz["head_dim"]),
+                                     "softcap": 30.0, "v_mix": True, "vdim": sz["head_dim"]}})
+    return {"architecture": "Gufotar", "layers": layers, "max_positions": max_positions, "norm": {"eps": 1e-5},
+            "vocab": sz["vocab"], "width": sz["width"]}
+
+
+def build_gufotar(sz, batch, max_positions, dev, dtype):
+    from lite_llama_b200.executor import ModelRunner
+    from lite_llama_b200.executor.layered_decoder import map_gufotar_weights, parse_gufotar_config, random_gufotar_tensors
+
+    conf = parse_gufotar_config(gufotar_config(sz, max_positions))
+    conf.validate()
+    weights = map_gufotar_weights(conf, random_gufotar_tensors(conf, seed=0), dev, dtype)
+    return ModelRunner(conf, weights, batch * max_positions, device=dev, dtype=dtype, max_requests=batch)
+
+
+def build_uniform(sz, batch, max_positions, dev, dtype):
+    from lite_llama_b200.executor import ModelConfig, ModelRunner
+
+    cfg = ModelConfig("uniform-" + str(sz["width"]), sz["width"], sz["layers"], sz["heads"], sz["kv_heads"],
+                      sz["head_dim"], sz["ff"], sz["vocab"])
+    return ModelRunner.build(cfg, max_seq_len=max_positions, max_gpu_num_blocks=batch * max_positions, device=dev,
+                             dtype=dtype, seed=0)
+
+
+def step_throughput(sz, batch, prompt, dev, dtype, flush) -> dict:
+    """tokens/s of a whole-prompt step (batch x prompt tokens) and of a decode step (batch x 1) for both models."""
+    max_pos = prompt + 64
+    out = {}
+    gen = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, sz["vocab"], (batch, prompt), generator=gen)
+    # ---- the layer-list design: ragged steps through ModelRunner.forward_ragged
+    r = build_gufotar(sz, batch, max_pos, dev, dtype)
+    reqs = []
+
+    def g_prefill():
+        for q in reqs:
+            r.close_request(q)
+        reqs[:] = [r.open_request() for _ in range(batch)]
+        return r.forward_ragged([(q, ids[i].tolist()) for i, q in enumerate(reqs)])
+
+    pre = timed(g_prefill, flush, warmup=2, reps=3)
+    tok = [[int(t)] for t in torch.randint(0, sz["vocab"], (batch,), generator=gen)]
+    state = {"n": 0}
+
+    def g_decode():
+        if state["n"] >= 48:                      # stay inside the position table: start over from the prompt
+            g_prefill()
+            state["n"] = 0
+        state["n"] += 1
+        return r.forward_ragged([(q, tok[i]) for i, q in enumerate(reqs)])
+
+    dec = timed(g_decode, flush, warmup=3, reps=9)
+    out["gufotar"] = {"prefill_ms": pre, "prefill_tok_s": batch * prompt / pre * 1e3, "decode_ms": dec,
+                      "decode_tok_s": batch / dec * 1e3, "weight_bytes_per_step": r.model.w.nbytes_per_step()}
+    del r, reqs
+    torch.cuda.empty_cache()
+    # ---- the closest existing model: uniform rotary decoder, padded-rectangle prefill + one-token decode (eager)
+    u = build_uniform(sz, batch, max_pos, dev, dtype)
+    lens = torch.full((batch,), prompt, dtype=torch.int64, device=dev)
+    idx = torch.arange(batch, dtype=torch.int64, device=dev)
+    pos = torch.arange(prompt, device=dev).repeat(batch, 1)
+    dids = ids.to(dev)
+
+    def u_prefill():
+        u.kv_cache_manager.free_all()
+        u.prefill_alloc_kv_cache(prompt, lens.clone(), idx)
+        return u.forward(dids, pos, last_token_index=lens - 1)
+
+    pre = timed(u_prefill, flush, warmup=2, reps=3)
+    one = dids[:, :1].contiguous()
+    ustate = {"n": 0}
+
+    def u_decode():
+        if ustate["n"] >= 48:
+            u_prefill()
+            ustate["n"] = 0
+        ustate["n"] += 1
+        u.decode_alloc_kv_cache(batch)
+        return u.forward(one, (u.atten_info.b_seq_len - 1).view(batch, 1))
+
+    dec = timed(u_decode, flush, warmup=3, reps=9)
+    out["uniform_decoder"] = {"prefill_ms": pre, "prefill_tok_s": batch * prompt / pre * 1e3, "decode_ms": dec,
+                              "decode_tok_s": batch / dec * 1e3, "weight_bytes_per_step": u.model.w.nbytes_per_step()}
+    del u
+    torch.cuda.empty_cache()
+    return out
+
+
+def kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) -> list[dict]:
+    """Every kernel of the new path alone, at the size's shapes, beside its like kernel of the uniform decoder.
+    ``frac`` = achieved / measured peak (HBM copy bandwidth for the bandwidth-bound ones, cuBLAS bf16 for attention
+    over prompts); ``bytes`` / ``flops`` are the algorithmic minimum of one launch."""
+    import lite_llama_b200.kernels as K
+
+    es = 2
+    W, H, G, D, ff = sz["width"], sz["heads"], sz["kv_heads"], sz["head_dim"], sz["ff"]
+    SH, SP, SN, SG = sz["s_heads"], sz["s_dim"], sz["s_state"], sz["s_groups"]
+    inner, gn = SH * SP, SG * SN
+    T, ctx = batch * prompt, prompt
+    rows: list[dict] = []
+
+    def i32(v):
+        return torch.tensor(list(v), dtype=torch.int32, device=dev)
+
+    def rnd(*shape, dt=dtype, s=1.0):
+        return (torch.randn(*shape, device=dev) * s).to(dt)
+
+    def add(name, like, fn, nbytes=0, flops=0, like_fn=None, like_bytes=None, like_flops=None):
+        ms = timed(fn, flush)
+        row = {"kernel": name, "us": ms * 1e3}
+        if flops:
+            row.update(tflops=flops / ms / 1e9, frac=flops / ms / 1e9 / tflops, bound="tensor")
+        else:
+            row.update(gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / hbm_gbs, bound="hbm")
+        if like_fn is not None:
+            lms = timed(like_fn, flush)
+            lf = (like_flops if like_flops is not None else flops)
+            lb = (like_bytes if like_bytes is not None else nbytes)
+            lfrac = lf / lms / 1e9 / tflops if flops else lb / lms / 1e6 / hbm_gbs
+            row.update(like=like, like_us=lms * 1e3, like_frac=lfrac, distance_ratio=(lfrac / row["frac"]) if row["frac"] else None)
+        rows.append(row)
+
+    # ---------------- per-sequence metadata for a prompt step and for a decode step
+    p_start, p_ctx, p_slot = i32(range(0, T + 1, prompt)), i32([0] * batch), i32(range(batch))
+    d_start, d_ctx = i32(range(batch + 1)), i32([ctx] * batch)
+    # ---------------- residual stream
+    resid = torch.randn(T, W, device=dev)
+    y, wn = rnd(T, W), rnd(W, s=0.1)
+    xh, res16 = rnd(T, W), rnd(T, W)
+    add("post_norm_residual", "skip_rmsnorm", lambda: K.post_norm_residual(resid, y, wn, 1e-5),
+        nbytes=T * W * (4 + 4 + es + es), like_fn=lambda: K.skip_rmsnorm(xh, res16, wn, 1e-5), like_bytes=T * W * 4 * es)
+    up = rnd(T, ff)
+    gu = rnd(T, 2 * ff)
+    add("relu_squared", "swiglu_forward", lambda: K.relu_squared(up), nbytes=T * ff * 2 * es,
+        like_fn=lambda: K.swiglu_forward(gu[:, :ff], gu[:, ff:]), like_bytes=T * ff * 3 * es)
+    # ---------------- state-space mixer
+    proj = rnd(T, 2 * inner + 2 * gn + SH)
+    cw, cb = rnd(inner + 2 * gn, 4, s=0.5), rnd(inner + 2 * gn, s=0.1)
+    tail = torch.zeros(batch, 3, inner + 2 * gn, dtype=dtype, device=dev)
+    add("causal_conv_silu (prompts)", None, lambda: K.causal_conv_silu(proj, inner, inner + 2 * gn, cw, cb, tail, p_start, p_ctx, p_slot),
+        nbytes=T * (inner + 2 * gn) * 2 * es)
+    xbc = rnd(T, inner + 2 * gn, s=0.5)
+    dtb, alog, dsk = rnd(SH), rnd(SH, s=0.5), rnd(SH)
+    st = torch.zeros(batch, SH, SP, SN, device=dev)
+    dt_view = proj[:, 2 * inner + 2 * gn:]
+    scan_bytes = T * ((inner + 2 * gn) * es + SH * es + inner * 4)
+    add("ssm_scan (prompts)", None, lambda: K.ssm_scan(xbc, dt_view, dtb, alog, dsk, st, p_start, p_ctx, p_slot, SH, SG, SN, SP),
+        nbytes=scan_bytes + batch * SH * SP * SN * 4)
+    add("ssm_scan (decode)", None, lambda: K.ssm_scan(xbc[:batch], dt_view[:batch], dtb, alog, dsk, st, d_start, d_ctx, p_slot, SH, SG, SN, SP),
+        nbytes=batch * SH * SP * SN * 8)
+    yf = torch.randn(T, inner, device=dev)
+    add("gated_group_norm", "skip_rmsnorm", lambda: K.gated_group_norm(yf, proj[:, :inner], rnd(inner), SG, 1e-5),
+        nbytes=T * inner * (4 + es + es), like_fn=lambda: K.skip_rmsnorm(xh, res16, wn, 1e-5), like_bytes=T * W * 4 * es)
+    # ---------------- attention: pool shared by both kernels, [K heads | V heads] per row
+    kvw = G * 2 * D
+    pool = rnd(batch * (ctx + 1), kvw, s=0.5)
+    table = torch.arange(batch * (ctx + 1), dtype=torch.int32, device=dev).view(batch, ctx + 1)
+    qkv = rnd(T, (H + 2 * G) * D, s=0.5)
+    qw, kw = rnd(H * D, s=0.1) + 1, rnd(G * D, s=0.1) + 1
+    rows_p = (table[:, :ctx]).reshape(-1).contiguous()
+    pos_p = i32(list(range(prompt)) * batch)
+    cos = rnd(batch, prompt, D)
+    add("attn_prepare", "rope_kv_write", lambda: K.attn_prepare(qkv, pool, rows_p, pos_p, H * D, G * D, G * D, qw, kw, 1e-5, 0.5, 64.0),
+        nbytes=T * ((2 * H + 2 * G) * D * es + 2 * G * D * es),
+        like_fn=lambda: K.rope_kv_write(qkv[:, :H * D].view(T, H, D), qkv[:, H * D:(H + G) * D].view(T, G, D),
+                                        qkv[:, (H + G) * D:].view(T, G, D), cos, cos, rows_p, pool.view(-1, 2 * G, D), batch, prompt))
+    sink = rnd(H)
+    out = torch.empty(T, H * D, dtype=dtype, device=dev)
+    att_flops = 4 * batch * H * D * prompt * (prompt + 1) / 2
+    scale = 1.0 / math.sqrt(D)
+    q3, k3, v3 = qkv[:, :H * D].view(T, H, D), qkv[:, H * D:(H + G) * D].view(T, G, D), qkv[:, (H + G) * D:].view(T, G, D)
+    lens = torch.full((batch,), prompt, dtype=torch.int32, device=dev)
+    add("sink_attention (prompts)", "flash_attention2_no_pad",
+        lambda: K.sink_attention(out, qkv, pool, table, p_start, p_ctx, p_slot, None, batch, prompt, sink, H, G, D, D, scale, 30.0),
+        flops=att_flops,
+        like_fn=lambda: K.flash_attention2_no_pad(q3, k3, v3, scale * 1.4426950408889634, p_start[:batch], lens, prompt))
+    splits = max(1, min(64, -(-(ctx + 1) // 256)))
+    per = -(-(-(-(ctx + 1) // splits)) // 32) * 32
+    dec_bytes = batch * (ctx + 1) * kvw * es
+    seq1 = torch.full((batch,), ctx + 1, dtype=torch.int32, device=dev)
+    add("sink_attention (decode)", "flash_decoding",
+        lambda: K.sink_attention(out, qkv, pool, table, d_start, d_ctx, p_slot, None, batch, 1, sink, H, G, D, D, scale, 30.0,
+                                 num_splits=splits, split_keys=per),
+        nbytes=dec_bytes,
+        like_fn=lambda: K.flash_decoding(q3[:batch], pool.view(-1, 2 * G, D)[:, :G], pool.view(-1, 2 * G, D)[:, G:], scale,
+                                         table, p_slot, seq1, ctx + 1))
+    return rows
+
+
+def run(args) -> None:
+    from bench import ClockSampler, peaks
+
+    dev = "cuda:0"
+    torch.cuda.set_device(0)
+    dtype = torch.bfloat16
+    hbm_gbs, tflops, src = peaks()
+    flush = _flush_buffer(dev)
+    sizes = [s for s in (args.design_sizes or "small,1b,8b").split(",") if s]
+    result = {"design": args.design, "dtype": "bf16", "data": "synthetic ids, random weights", "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": tflops, "source": src},
+              "batch": args.batch, "prompt_len": args.prompt_len, "l2_policy": "256 MiB written between timed runs", "sizes": {}}
+    t0 = time.time()
+    with ClockSampler(0) as clocks:
+        for name in sizes:
+            sz = SIZES[name]
+            entry = {"geometry": sz}
+            entry["steps"] = step_throughput(sz, args.batch, args.prompt_len, dev, dtype, flush)
+            torch.cuda.empty_cache()
+            entry["kernels"] = kernel_table(sz, args.batch, args.prompt_len, dev, dtype, flush, hbm_gbs, tflops)
+            torch.cuda.empty_cache()
+            result["sizes"][name] = entry
+    result["clocks"] = clocks.summary()
+    result["seconds"] = round(time.time() - t0, 1)
+    print(json.dumps(result))
