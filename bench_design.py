@@ -202,7 +202,7 @@ def kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) -> list[
         nbytes=T * (inner + 2 * gn) * 2 * es)
     xbc = rnd(T, inner + 2 * gn, s=0.5)
     dtb, alog, dsk = rnd(SH), rnd(SH, s=0.5), rnd(SH)
-    st = torch.zeros(batch, SH, SP, SN, device=dev)
+    st = torch.zeros(batch, SH, SN, SP, device=dev)
     dt_view = proj[:, 2 * inner + 2 * gn:]
     scan_bytes = T * ((inner + 2 * gn) * es + SH * es + inner * 4)
     add("ssm_scan (prompts)", None, lambda: K.ssm_scan(xbc, dt_view, dtb, alog, dsk, st, p_start, p_ctx, p_slot, SH, SG, SN, SP),

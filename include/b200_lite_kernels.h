@@ -281,7 +281,7 @@ int b2l_causal_conv_silu(void* out, const void* in, int64_t in_row_stride, const
                          void* tail, const void* seq_start, const void* seq_ctx, const void* seq_slot, int64_t num_seqs,
                          int64_t tokens, int channels, int taps, int dtype, void* stream);
 /* Scalar-decay state-space recurrence (csrc/ssm_scan.cu).  xbc rows = [x: heads*head_dim | B: groups*state | C: ...];
- * state_f32 [slots, heads, head_dim, state] fp32; y_f32 [tokens, heads*head_dim] fp32. */
+ * state_f32 [slots, heads, state, head_dim] fp32; y_f32 [tokens, heads*head_dim] fp32. */
 int b2l_ssm_scan(void* y_f32, void* state_f32, const void* xbc, int64_t xbc_row_stride, const void* dt_raw,
                  int64_t dt_row_stride, const void* dt_bias, const void* a_log, const void* d_skip,
                  const void* seq_start, const void* seq_ctx, const void* seq_slot, int64_t num_seqs, int heads,

@@ -7,8 +7,10 @@
 //                  position-dependent query gain, value mixing with an earlier layer's values, K|V cache write
 //   sink_attention sequence s brings q_len new tokens after ctx cached ones; token i sees cache positions 0..ctx+i
 //                  (its own K/V is already in the pool).  One launch covers a list of sequences:
-//                  * tiled mode: CTA = (token tile, kv head, sequence); the rows of a CTA (tokens x the kv head's
-//                    query heads) share every K/V tile that is staged in shared memory
+//                  * tiled mode, 16-bit T: CTA = (64 tokens, query head, sequence) on mma.sync tensor-core tiles
+//                  * tiled mode, fp32 T (or head sizes the tensor-core tiles do not take): CTA = (token tile, kv head,
+//                    sequence) on the CUDA cores; the rows of a CTA (tokens x the kv head's query heads) share every
+//                    K/V tile that is staged in shared memory
 //                  * split mode (one new token per sequence: decode): CTA = (key range, kv head, sequence), fp32
 //                    partial (max, sum, acc) per range, merged with the sink by sink_attention_merge
 // Softmax statistics, scores and the output accumulator are fp32 whatever T is.
@@ -150,6 +152,215 @@ __global__ void __launch_bounds__(kWarps * 32) sink_attention_kernel(AttnArgs a)
       }
     }
   }
+}
+
+// ---- tiled mode on the tensor cores (16-bit T) ------------------------------------------------------------------
+// CTA = 64 new tokens of one (sequence, query head); 4 warps x 16 query rows (FlashAttention-2 schedule, the same
+// fragment handling as flash_attention_nopad.cu).  64-key K and V tiles are gathered through the request table with
+// 16-byte loads into padded shared memory (head sizes are padded to DP / DVP columns of zeros), S = Q K^T and
+// O += P V run on mma.sync m16n8k16 with fp32 accumulators, the soft cap is applied to the fp32 scores, the online
+// softmax works in the log2 domain, the sink joins the denominator once at the end.  Keys 0 .. ctx + t (cached prefix
+// + the portion itself) are visible to token t.  Needs D, Dv multiples of 8 and <= 128, 16-byte aligned pool rows.
+constexpr int kTileM = 64, kTileN = 64;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <typename T, int DP, int DVP>
+__global__ void __launch_bounds__(128) sink_attention_mma_kernel(AttnArgs a) {
+  pdl_prologue();
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  constexpr int KP = (DP + 8) * 2, VP = (DVP + 8) * 2;          // row pitches in bytes
+  uint8_t* ks_ptr = smem_raw;
+  uint8_t* vs_ptr = smem_raw + kTileN * KP;
+  const int D = a.D, Dv = a.Dv, per = a.H / a.G;
+  const int z = blockIdx.z, s = a.seq_list ? a.seq_list[z] : z;
+  const int start = a.seq_start[s], qlen = a.seq_start[s + 1] - start, ctx = a.seq_ctx[s];
+  const int t0 = blockIdx.x * kTileM;
+  if (t0 >= qlen) return;
+  const int t_count = min(kTileM, qlen - t0);
+  const int h = blockIdx.y, g = h / per;
+  const int64_t slot = a.seq_slot[s];
+  const int key_hi = ctx + t0 + t_count;                         // exclusive
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int gq = lane >> 2, tq = lane & 3;
+  const int r0 = warp * 16 + gq, r1 = r0 + 8;                    // rows of the tile
+  const bool ok0 = r0 < t_count, ok1 = r1 < t_count;
+  const int pos0 = ctx + t0 + r0, pos1 = ctx + t0 + r1;          // last visible key of each row
+  const T* q = (const T*)a.q;
+  const T* kv = (const T*)a.kv;
+  uint32_t qf[DP / 16][4];
+  {
+    const T* q0 = q + (int64_t)(start + t0 + (ok0 ? r0 : 0)) * a.q_stride + h * D;
+    const T* q1 = q + (int64_t)(start + t0 + (ok1 ? r1 : 0)) * a.q_stride + h * D;
+#pragma unroll
+    for (int kk = 0; kk < DP / 16; ++kk) {
+      const int c = kk * 16 + 2 * tq;
+      qf[kk][0] = (ok0 && c < D) ? *reinterpret_cast<const uint32_t*>(q0 + c) : 0u;
+      qf[kk][1] = (ok1 && c < D) ? *reinterpret_cast<const uint32_t*>(q1 + c) : 0u;
+      qf[kk][2] = (ok0 && c + 8 < D) ? *reinterpret_cast<const uint32_t*>(q0 + c + 8) : 0u;
+      qf[kk][3] = (ok1 && c + 8 < D) ? *reinterpret_cast<const uint32_t*>(q1 + c + 8) : 0u;
+    }
+  }
+  float o[DVP / 8][4];
+#pragma unroll
+  for (int i = 0; i < DVP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const int warp_last = ctx + t0 + warp * 16 + 15;
+  const int* trow = a.table + slot * a.table_stride;
+  const float cap = a.softcap, inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
+  const uint32_t ks = smem_u32(ks_ptr), vs = smem_u32(vs_ptr);
+  for (int k0 = 0; k0 < key_hi; k0 += kTileN) {
+    __syncthreads();
+    for (int i = tid; i < kTileN * (DP / 8); i += 128) {
+      const int r = i / (DP / 8), c = (i - r * (DP / 8)) * 8;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (k0 + r < key_hi && c < D) v = ldg_128(kv + (int64_t)trow[k0 + r] * a.kv_stride + g * D + c);
+      *reinterpret_cast<uint4*>(ks_ptr + r * KP + c * 2) = v;
+    }
+    for (int i = tid; i < kTileN * (DVP / 8); i += 128) {
+      const int r = i / (DVP / 8), c = (i - r * (DVP / 8)) * 8;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (k0 + r < key_hi && c < Dv) v = ldg_128(kv + (int64_t)trow[k0 + r] * a.kv_stride + a.G * D + g * Dv + c);
+      *reinterpret_cast<uint4*>(vs_ptr + r * VP + c * 2) = v;
+    }
+    __syncthreads();
+    if (k0 > warp_last) continue;                                // warp-uniform: the tile is above this warp's rows
+    float sc[kTileN / 8][4];
+#pragma unroll
+    for (int j = 0; j < kTileN / 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+    {
+      const int mj = lane >> 3, r = lane & 7;
+      const uint32_t a0 = ks + ((mj >> 1) * 8 + r) * KP + (mj & 1) * 16;
+#pragma unroll
+      for (int kk = 0; kk < DP / 16; ++kk) {
+#pragma unroll
+        for (int jp = 0; jp < kTileN / 16; ++jp) {
+          uint32_t bf[4];
+          ldmatrix_x4(bf, a0 + jp * 16 * KP + kk * 32);
+          mma_m16n8k16<T>(sc[2 * jp], qf[kk], bf[0], bf[1]);
+          mma_m16n8k16<T>(sc[2 * jp + 1], qf[kk], bf[2], bf[3]);
+        }
+      }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < kTileN / 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = k0 + j * 8 + 2 * tq + (e & 1);
+        const int lim = (e >> 1) ? pos1 : pos0;
+        float v = sc[j][e] * a.scale;
+        if (cap > 0.f) v = cap * tanhf(v * inv_cap);
+        v = key <= lim ? v * kLog2e : -INFINITY;
+        sc[j][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    }
+    float alpha[2], base[2];
+#pragma unroll
+    for (int r2 = 0; r2 < 2; ++r2) {
+      mx[r2] = fmaxf(mx[r2], __shfl_xor_sync(0xffffffffu, mx[r2], 1));
+      mx[r2] = fmaxf(mx[r2], __shfl_xor_sync(0xffffffffu, mx[r2], 2));
+      const float mnew = fmaxf(m_run[r2], mx[r2]);
+      base[r2] = mnew == -INFINITY ? 0.f : mnew;
+      alpha[r2] = fast_exp2(m_run[r2] - base[r2]);
+      m_run[r2] = mnew;
+    }
+    float ps[2] = {0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < kTileN / 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pv = fast_exp2(sc[j][e] - base[e >> 1]);
+        sc[j][e] = pv;
+        ps[e >> 1] += pv;
+      }
+    }
+    l_run[0] = l_run[0] * alpha[0] + ps[0];
+    l_run[1] = l_run[1] * alpha[1] + ps[1];
+#pragma unroll
+    for (int i = 0; i < DVP / 8; ++i) {
+      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+    }
+    {
+      const int mj = lane >> 3, r = lane & 7;
+      const uint32_t a0 = vs + ((mj & 1) * 8 + r) * VP + (mj >> 1) * 16;
+#pragma unroll
+      for (int kt = 0; kt < kTileN / 16; ++kt) {
+        uint32_t pf[4];
+        pf[0] = pack2<T>(sc[2 * kt][0], sc[2 * kt][1]);
+        pf[1] = pack2<T>(sc[2 * kt][2], sc[2 * kt][3]);
+        pf[2] = pack2<T>(sc[2 * kt + 1][0], sc[2 * kt + 1][1]);
+        pf[3] = pack2<T>(sc[2 * kt + 1][2], sc[2 * kt + 1][3]);
+#pragma unroll
+        for (int dn = 0; dn < DVP / 16; ++dn) {
+          uint32_t bf[4];
+          ldmatrix_x4_trans(bf, a0 + kt * 16 * VP + dn * 32);
+          mma_m16n8k16<T>(o[2 * dn], pf, bf[0], bf[1]);
+          mma_m16n8k16<T>(o[2 * dn + 1], pf, bf[2], bf[3]);
+        }
+      }
+    }
+  }
+  float inv[2];
+#pragma unroll
+  for (int r2 = 0; r2 < 2; ++r2) {
+    l_run[r2] += __shfl_xor_sync(0xffffffffu, l_run[r2], 1);
+    l_run[r2] += __shfl_xor_sync(0xffffffffu, l_run[r2], 2);
+    float num = 1.f, den = l_run[r2];
+    if (a.sink) {
+      const float sk = to_f32(((const T*)a.sink)[h]) * kLog2e;
+      const float mf = fmaxf(m_run[r2], sk);
+      num = fast_exp2(m_run[r2] - mf);
+      den = l_run[r2] * num + fast_exp2(sk - mf);
+    }
+    inv[r2] = num / den;
+  }
+  T* ob = (T*)a.out + h * Dv;
+  if (ok0) {
+    T* orow = ob + (int64_t)(start + t0 + r0) * a.out_stride;
+#pragma unroll
+    for (int i = 0; i < DVP / 8; ++i)
+      if (i * 8 + 2 * tq < Dv) *reinterpret_cast<uint32_t*>(orow + i * 8 + 2 * tq) = pack2<T>(o[i][0] * inv[0], o[i][1] * inv[0]);
+  }
+  if (ok1) {
+    T* orow = ob + (int64_t)(start + t0 + r1) * a.out_stride;
+#pragma unroll
+    for (int i = 0; i < DVP / 8; ++i)
+      if (i * 8 + 2 * tq < Dv) *reinterpret_cast<uint32_t*>(orow + i * 8 + 2 * tq) = pack2<T>(o[i][2] * inv[1], o[i][3] * inv[1]);
+  }
+}
+
+template <typename T, int DP, int DVP>
+int launch_attention_mma(const AttnArgs& a, int max_q_len, int64_t num_seqs, cudaStream_t st) {
+  constexpr int smem = kTileN * ((DP + 8) * 2 + (DVP + 8) * 2);
+  static int cache[64] = {0};
+  B2L_CUDA_CHECK(b2l_ensure_dynamic_smem(sink_attention_mma_kernel<T, DP, DVP>, smem, cache));
+  const dim3 grid((unsigned)((max_q_len + kTileM - 1) / kTileM), (unsigned)a.H, (unsigned)num_seqs);
+  b2l_launch(sink_attention_mma_kernel<T, DP, DVP>, grid, dim3(128), (size_t)smem, st, a);
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}
+
+template <typename T>
+int dispatch_attention_mma(const AttnArgs& a, int max_q_len, int64_t num_seqs, cudaStream_t st) {
+  const int dp = a.D <= 32 ? 32 : (a.D <= 64 ? 64 : 128), dvp = a.Dv <= 32 ? 32 : (a.Dv <= 64 ? 64 : 128);
+#define B2L_MMA(P, V) if (dp == P && dvp == V) return launch_attention_mma<T, P, V>(a, max_q_len, num_seqs, st)
+  B2L_MMA(32, 32); B2L_MMA(32, 64); B2L_MMA(32, 128);
+  B2L_MMA(64, 32); B2L_MMA(64, 64); B2L_MMA(64, 128);
+  B2L_MMA(128, 32); B2L_MMA(128, 64); B2L_MMA(128, 128);
+#undef B2L_MMA
+  B2L_UNSUPPORTED("sink_attention: head sizes %d / %d", a.D, a.Dv);
+}
+
+// the tensor-core tiled kernel takes 16-bit activations, head sizes in 8-element steps up to 128, and pool / q rows
+// whose 16-byte vectors are aligned
+inline bool mma_path_ok(const AttnArgs& a, int dtype) {
+  if (dtype != B2L_F16 && dtype != B2L_BF16) return false;
+  if (a.D % 8 || a.Dv % 8 || a.D > 128 || a.Dv > 128) return false;
+  if (a.kv_stride % 8 || a.q_stride % 2 || a.out_stride % 2) return false;
+  if (((uintptr_t)a.kv % 16) || ((uintptr_t)a.q % 4) || ((uintptr_t)a.out % 4)) return false;
+  return true;
 }
 
 template <typename T>
@@ -317,6 +528,10 @@ extern "C" int b2l_sink_attention(void* out, int64_t out_row_stride, const void*
     });
     B2L_LAUNCH_CHECK();
     return B2L_OK;
+  }
+  if (mma_path_ok(a, dtype)) {
+    if (dtype == B2L_F16) return dispatch_attention_mma<__half>(a, max_q_len, num_seqs, st);
+    return dispatch_attention_mma<__nv_bfloat16>(a, max_q_len, num_seqs, st);
   }
   const dim3 grid((unsigned)((max_q_len + a.BQ - 1) / a.BQ), (unsigned)(kv_heads * hchunks), (unsigned)num_seqs);
   int rc = B2L_OK;

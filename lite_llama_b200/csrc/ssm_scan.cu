@@ -7,6 +7,7 @@
 //   conv_tail_update      the slot's conv tail after the step (in place)
 //   ssm_scan              dt = softplus(dt_raw + dt_bias); S <- exp(-exp(A_log) dt) S + dt B x^T; y = S^T C + D x
 //                         S in fp32 registers for the whole step, read from / written to the slot once
+//                         (slot layout [head, n, p])
 //   gated_group_norm      o = unit_rms_g(y * silu(z)) * w   in `groups` equal parts of the row
 // A sequence with seq_ctx == 0 starts from zero: its slot is never read, so slots need no clearing when reused.
 #include "common.cuh"
@@ -72,86 +73,136 @@ __global__ void conv_tail_update_kernel(T* __restrict__ tail, const T* __restric
   }
 }
 
-// One warp = kCols columns p of one head; lane l holds state rows n = l + 32 j.  grid (ceil(P / (4 kCols)), H, nseq).
-constexpr int kCols = 4, kScanWarps = 4;
+// Scan: one CTA = (tile of 32 * ctiles columns p, head, sequence).  Lane = column, so y_t[p] = sum_n S[n, p] C_t[n]
+// needs no cross-lane reduction; a compute warp keeps NPT state rows of its 32 columns in registers, and when N > NPT
+// the rows are cut into `nslices` warps whose partial sums meet in shared memory once per chunk of kChunk tokens
+// (fixed slice order: deterministic).  The scan of one sequence is serial, so latency decides: kLoadWarps extra warps
+// stage the NEXT chunk's B_t, C_t, x_t (as fp32) and dt / decay into the other half of a double buffer while the
+// compute warps run the current one; the compute warps read them as broadcast float4.
+// State layout: [slot, head, n, p] (p contiguous = coalesced per n).
+constexpr int kChunk = 16;
+constexpr int kLoadWarps = 4;
 
-template <typename T, int NJ>
-__global__ void __launch_bounds__(kScanWarps * 32) ssm_scan_kernel(
+template <typename T, int NPT>
+__global__ void __launch_bounds__(512) ssm_scan_kernel(
     float* __restrict__ y, float* __restrict__ state, const T* __restrict__ xbc, int64_t xbc_stride,
     const T* __restrict__ dt_raw, int64_t dt_stride, const T* __restrict__ dt_bias, const T* __restrict__ a_log,
     const T* __restrict__ d_skip, const int* __restrict__ seq_start, const int* __restrict__ seq_ctx,
-    const int* __restrict__ seq_slot, int heads, int groups, int N, int P) {
+    const int* __restrict__ seq_slot, int heads, int groups, int N, int P, int ctiles, int nslices) {
   pdl_prologue();
-  const int s = blockIdx.z, h = blockIdx.y;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int p0 = (blockIdx.x * kScanWarps + warp) * kCols;
-  if (p0 >= P) return;
+  extern __shared__ __align__(16) float sm[];
+  const int Np = nslices * NPT, cols = ctiles * 32;
+  const int stage_floats = 2 * kChunk * Np + kChunk * cols + 2 * kChunk;
+  float* sYbase = sm + 2 * stage_floats;       // [2][nslices][kChunk][cols], nslices > 1 only
+  const int s = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * cols;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int cwarps = ctiles * nslices;
+  const bool computes = warp < cwarps;
+  const int ct = warp / nslices, sl = warp - ct * nslices;
+  const int col = col0 + ct * 32 + lane, n0 = sl * NPT;
   const int start = seq_start[s], len = seq_start[s + 1] - start, ctx = seq_ctx[s];
   if (len <= 0) return;
   const int64_t slot = seq_slot[s];
   const int g = h / (heads / groups), inner = heads * P;
   const float neg_a = -expf(to_f32(a_log[h])), bias = to_f32(dt_bias[h]), dsk = to_f32(d_skip[h]);
-  float* st = state + ((slot * heads + h) * (int64_t)P) * N;            // [P, N], n contiguous
-  float S[kCols][NJ];
-#pragma unroll
-  for (int c = 0; c < kCols; ++c)
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-      const int n = lane + 32 * j;
-      S[c][j] = (ctx > 0 && n < N && p0 + c < P) ? st[(int64_t)(p0 + c) * N + n] : 0.f;
-    }
-  const T* xrow = xbc + (int64_t)start * xbc_stride;
   const int boff = inner + g * N, coff = inner + groups * N + g * N;
-  // software pipeline: the next token's operands are in flight while this token's state update runs
-  float nb[NJ], nc[NJ], nx[kCols], ndt;
-  auto fetch = [&](int t) {
-    const T* r = xrow + (int64_t)t * xbc_stride;
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-      const int n = lane + 32 * j;
-      nb[j] = n < N ? to_f32(r[boff + n]) : 0.f;
-      nc[j] = n < N ? to_f32(r[coff + n]) : 0.f;
+  const int nchunks = (len + kChunk - 1) / kChunk;
+
+  // stage chunk k into half k & 1 with `nth` threads numbered `t0`
+  auto stage = [&](int k, int t0, int nth) {
+    float* sB = sm + (k & 1) * stage_floats;
+    float* sC = sB + kChunk * Np;
+    float* sX = sC + kChunk * Np;
+    float* sDt = sX + kChunk * cols;
+    const int c0 = k * kChunk, tc = min(kChunk, len - c0);
+    const T* rows = xbc + (int64_t)(start + c0) * xbc_stride;
+#pragma unroll 8
+    for (int i = t0; i < tc * Np; i += nth) {
+      const int t = i / Np, n = i - t * Np;
+      const T* r = rows + (int64_t)t * xbc_stride;
+      const float bv = n < N ? to_f32(r[boff + n]) : 0.f;
+      const float cv = n < N ? to_f32(r[coff + n]) : 0.f;
+      sB[i] = bv;
+      sC[i] = cv;
     }
-#pragma unroll
-    for (int c = 0; c < kCols; ++c) nx[c] = (p0 + c < P) ? to_f32(r[h * P + p0 + c]) : 0.f;
-    ndt = to_f32(dt_raw[(int64_t)(start + t) * dt_stride + h]);
+#pragma unroll 8
+    for (int i = t0; i < tc * cols; i += nth) {
+      const int t = i / cols, c = i - t * cols;
+      sX[i] = (col0 + c < P) ? to_f32(rows[(int64_t)t * xbc_stride + h * P + col0 + c]) : 0.f;
+    }
+    if (t0 < tc) {
+      const float dtv = softplus_f(to_f32(dt_raw[(int64_t)(start + c0 + t0) * dt_stride + h]) + bias);
+      sDt[t0] = dtv;
+      sDt[kChunk + t0] = expf(neg_a * dtv);
+    }
   };
-  fetch(0);
-  for (int t = 0; t < len; ++t) {
-    float b[NJ], cc[NJ], x[kCols];
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) { b[j] = nb[j]; cc[j] = nc[j]; }
-#pragma unroll
-    for (int c = 0; c < kCols; ++c) x[c] = nx[c];
-    const float dt = softplus_f(ndt + bias);
-    if (t + 1 < len) fetch(t + 1);
-    const float decay = expf(neg_a * dt);
-    float acc[kCols];
-#pragma unroll
-    for (int c = 0; c < kCols; ++c) {
-      const float dx = dt * x[c];
-      float a = 0.f;
-#pragma unroll
-      for (int j = 0; j < NJ; ++j) {
-        S[c][j] = fmaf(decay, S[c][j], dx * b[j]);
-        a = fmaf(S[c][j], cc[j], a);
-      }
-      acc[c] = warp_reduce_sum(a);
+  // y of chunk k from the slices' partial sums (nslices > 1)
+  auto reduce = [&](int k, int t0, int nth) {
+    const float* sX = sm + (k & 1) * stage_floats + 2 * kChunk * Np;
+    const float* sY = sYbase + (k & 1) * nslices * kChunk * cols;
+    const int c0 = k * kChunk, tc = min(kChunk, len - c0);
+    for (int i = t0; i < tc * cols; i += nth) {
+      const int t = i / cols, c = i - t * cols;
+      if (col0 + c >= P) continue;
+      float v = 0.f;
+      for (int q = 0; q < nslices; ++q) v += sY[(q * kChunk + t) * cols + c];
+      y[(int64_t)(start + c0 + t) * inner + h * P + col0 + c] = fmaf(dsk, sX[i], v);
     }
-    if (lane < kCols && p0 + lane < P) {
-      float v = acc[0], xv = x[0];
+  };
+
+  float* st = state + ((slot * heads + h) * (int64_t)N) * P;            // [N, P]
+  float S[NPT];
+  if (computes) {
 #pragma unroll
-      for (int c = 1; c < kCols; ++c) if (lane == c) { v = acc[c]; xv = x[c]; }
-      y[(int64_t)(start + t) * inner + h * P + p0 + lane] = fmaf(dsk, xv, v);
-    }
+    for (int i = 0; i < NPT; ++i) S[i] = (ctx > 0 && n0 + i < N && col < P) ? st[(int64_t)(n0 + i) * P + col] : 0.f;
   }
+  stage(0, tid, blockDim.x);
+  __syncthreads();
+  for (int k = 0; k < nchunks; ++k) {
+    if (computes) {
+      const float* sB = sm + (k & 1) * stage_floats;
+      const float* sC = sB + kChunk * Np;
+      const float* sX = sC + kChunk * Np;
+      const float* sDt = sX + kChunk * cols;
+      float* sY = sYbase + (k & 1) * nslices * kChunk * cols;
+      const int c0 = k * kChunk, tc = min(kChunk, len - c0);
+      for (int t = 0; t < tc; ++t) {
+        const float dtv = sDt[t], dec = sDt[kChunk + t], xv = sX[t * cols + ct * 32 + lane];
+        const float dx = dtv * xv;
+        const float4* b4 = reinterpret_cast<const float4*>(sB + t * Np + n0);
+        const float4* c4 = reinterpret_cast<const float4*>(sC + t * Np + n0);
+        float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
-  for (int c = 0; c < kCols; ++c)
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-      const int n = lane + 32 * j;
-      if (n < N && p0 + c < P) st[(int64_t)(p0 + c) * N + n] = S[c][j];
+        for (int i = 0; i < NPT / 4; ++i) {
+          const float4 b = b4[i], c = c4[i];
+          S[4 * i + 0] = fmaf(dec, S[4 * i + 0], dx * b.x); acc0 = fmaf(S[4 * i + 0], c.x, acc0);
+          S[4 * i + 1] = fmaf(dec, S[4 * i + 1], dx * b.y); acc1 = fmaf(S[4 * i + 1], c.y, acc1);
+          S[4 * i + 2] = fmaf(dec, S[4 * i + 2], dx * b.z); acc0 = fmaf(S[4 * i + 2], c.z, acc0);
+          S[4 * i + 3] = fmaf(dec, S[4 * i + 3], dx * b.w); acc1 = fmaf(S[4 * i + 3], c.w, acc1);
+        }
+        const float acc = acc0 + acc1;
+        if (nslices == 1) {
+          if (col < P) y[(int64_t)(start + c0 + t) * inner + h * P + col] = fmaf(dsk, xv, acc);
+        } else {
+          sY[(sl * kChunk + t) * cols + ct * 32 + lane] = acc;
+        }
+      }
+    } else {
+      const int t0 = tid - cwarps * 32, nth = kLoadWarps * 32;
+      if (nslices > 1 && k > 0) {
+        reduce(k - 1, t0, nth);                 // reads the half that chunk k + 1 is about to overwrite
+        asm volatile("bar.sync 1, %0;" ::"n"(kLoadWarps * 32) : "memory");
+      }
+      if (k + 1 < nchunks) stage(k + 1, t0, nth);
     }
+    __syncthreads();
+  }
+  if (nslices > 1) reduce(nchunks - 1, tid, blockDim.x);
+  if (computes) {
+#pragma unroll
+    for (int i = 0; i < NPT; ++i)
+      if (n0 + i < N && col < P) st[(int64_t)(n0 + i) * P + col] = S[i];
+  }
 }
 
 template <typename T>
@@ -212,21 +263,34 @@ extern "C" int b2l_ssm_scan(void* y_f32, void* state_f32, const void* xbc, int64
               "ssm_scan: null pointer");
   B2L_REQUIRE(heads > 0 && groups > 0 && heads % groups == 0 && state_size > 0 && head_dim > 0,
               "ssm_scan: bad geometry heads=%d groups=%d state=%d head_dim=%d", heads, groups, state_size, head_dim);
-  B2L_REQUIRE(state_size <= 256, "ssm_scan: state size %d > 256", state_size);
+  B2L_REQUIRE(state_size <= 768, "ssm_scan: state size %d > 768", state_size);
   if (num_seqs <= 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  const dim3 block(kScanWarps * 32), grid((unsigned)cdiv64(head_dim, kScanWarps * kCols), (unsigned)heads,
-                                          (unsigned)num_seqs);
-  const int nj = (state_size + 31) / 32;
-#define B2L_SCAN(NJV)                                                                                                \
-  b2l_launch(ssm_scan_kernel<T, NJV>, grid, block, (size_t)0, st, (float*)y_f32, (float*)state_f32, (const T*)xbc,   \
-             xbc_row_stride, (const T*)dt_raw, dt_row_stride, (const T*)dt_bias, (const T*)a_log, (const T*)d_skip,  \
-             (const int*)seq_start, (const int*)seq_ctx, (const int*)seq_slot, heads, groups, state_size, head_dim)
+  const int npt = state_size <= 16 ? 16 : (state_size <= 32 ? 32 : 64);
+  const int nslices = (state_size + npt - 1) / npt;
+  int ctiles = (head_dim + 31) / 32;
+  const int room = 8 / nslices > 1 ? 8 / nslices : 1;      // compute warps <= 12 with the 4 loaders: <= 512 threads
+  if (ctiles > room) ctiles = room;
+  const int cols = ctiles * 32, np = nslices * npt;
+  const size_t smem = (size_t)(2 * (2 * kChunk * np + kChunk * cols + 2 * kChunk) +
+                               (nslices > 1 ? 2 * nslices * kChunk * cols : 0)) * sizeof(float);
+  B2L_REQUIRE((int64_t)smem <= b2l_max_smem_optin(), "ssm_scan: state size %d needs %lld bytes of shared memory",
+              state_size, (long long)smem);
+  const dim3 block((ctiles * nslices + kLoadWarps) * 32), grid((unsigned)cdiv64(head_dim, cols), (unsigned)heads,
+                                                               (unsigned)num_seqs);
+#define B2L_SCAN(NPTV)                                                                                               \
+  do {                                                                                                               \
+    static int cache[64] = {0};                                                                                      \
+    B2L_CUDA_CHECK(b2l_ensure_dynamic_smem(ssm_scan_kernel<T, NPTV>, (int)smem, cache));                             \
+    b2l_launch(ssm_scan_kernel<T, NPTV>, grid, block, smem, st, (float*)y_f32, (float*)state_f32, (const T*)xbc,     \
+               xbc_row_stride, (const T*)dt_raw, dt_row_stride, (const T*)dt_bias, (const T*)a_log,                  \
+               (const T*)d_skip, (const int*)seq_start, (const int*)seq_ctx, (const int*)seq_slot, heads, groups,    \
+               state_size, head_dim, ctiles, nslices);                                                               \
+  } while (0)
   B2L_DISPATCH_FLOAT(dtype, "ssm_scan", {
-    if (nj <= 1) B2L_SCAN(1);
-    else if (nj <= 2) B2L_SCAN(2);
-    else if (nj <= 4) B2L_SCAN(4);
-    else B2L_SCAN(8);
+    if (npt == 16) B2L_SCAN(16);
+    else if (npt == 32) B2L_SCAN(32);
+    else B2L_SCAN(64);
   });
 #undef B2L_SCAN
   B2L_LAUNCH_CHECK();

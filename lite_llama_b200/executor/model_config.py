@@ -100,7 +100,7 @@ class Mamba2Spec:
         return 2 * self.inner + 2 * self.groups * self.state + self.heads
 
     def validate(self) -> None:
-        if self.heads % self.groups or self.inner % self.norm_groups or self.conv < 1 or self.state > 256:
+        if self.heads % self.groups or self.inner % self.norm_groups or self.conv < 1 or self.state > 768:
             raise ValueError(f"unsupported state-space mixer geometry: {self}")
 
 

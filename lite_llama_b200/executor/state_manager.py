@@ -1,5 +1,5 @@
 """Fixed-slot store for recurrent mixers, the counterpart of the KV pool for layers whose memory does not grow
-with the sequence: per recurrent layer one fp32 state tensor ``[slots, heads, head_dim, state]`` and one convolution
+with the sequence: per recurrent layer one fp32 state tensor ``[slots, heads, state, head_dim]`` and one convolution
 tail ``[slots, taps - 1, channels]`` (the last inputs of the short convolution, in the activation dtype).
 
 A request holds one slot from admission to release; the same slot number indexes the request -> rows table of the
@@ -24,7 +24,7 @@ class RecurrentStateManager:
         for i in config.recurrent_layers():
             m = config.layers[i].mixer
             assert isinstance(m, Mamba2Spec)
-            self.ssm_state[i] = torch.zeros((num_slots, m.heads, m.head_dim, m.state), dtype=torch.float32, device=device)
+            self.ssm_state[i] = torch.zeros((num_slots, m.heads, m.state, m.head_dim), dtype=torch.float32, device=device)
             self.conv_tail[i] = torch.zeros((num_slots, max(m.conv - 1, 1), m.conv_channels), dtype=dtype, device=device)
         self._free = list(range(num_slots - 1, -1, -1))
         self._held: set[int] = set()

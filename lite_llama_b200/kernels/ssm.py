@@ -26,7 +26,7 @@ def causal_conv_silu(proj: torch.Tensor, col: int, channels: int, weight: torch.
 @torch.no_grad()
 def ssm_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias, a_log, d_skip, state: torch.Tensor,
              seq_start, seq_ctx, seq_slot, heads: int, groups: int, state_size: int, head_dim: int) -> torch.Tensor:
-    """``y [tokens, heads*head_dim]`` fp32; ``state [slots, heads, head_dim, state_size]`` fp32 advanced in place.
+    """``y [tokens, heads*head_dim]`` fp32; ``state [slots, heads, state_size, head_dim]`` fp32 advanced in place.
     ``dt_raw`` is a column view ``[tokens, heads]`` of the input projection (row stride kept)."""
     require_cuda(xbc, dt_raw, state)
     if state.dtype != torch.float32:

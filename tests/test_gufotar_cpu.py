@@ -117,7 +117,7 @@ def test_state_slots_change_hands():
 
     conf = parse_gufotar_config(O.make_config([O.attention_layer(), O.mamba2_layer(heads=4, vdim=5, state=9, groups=2, conv=3)]))
     sm = RecurrentStateManager(conf, 3, torch.bfloat16, device="cpu")
-    assert sm.ssm_state[1].shape == (3, 4, 5, 9) and sm.ssm_state[1].dtype == torch.float32
+    assert sm.ssm_state[1].shape == (3, 4, 9, 5) and sm.ssm_state[1].dtype == torch.float32
     assert sm.conv_tail[1].shape == (3, 2, 20 + 2 * 18) and 0 not in sm.ssm_state
     held = [sm.acquire() for _ in range(3)]
     assert sorted(held) == [0, 1, 2] and sm.free_slots == 0

@@ -103,7 +103,7 @@ def test_ssm_scan_carries_state_between_steps(heads, groups, state, hd):
     y_ref, s_ref = O.ssm_recurrence(xbc[:, :inner].double().view(T, heads, hd), O.softplus(dt_raw.double() + dt_bias.double()),
                                     a_log.double(), xbc[:, inner:inner + gn].double().view(T, groups, state),
                                     xbc[:, inner + gn:].double().view(T, groups, state), d.double())
-    st = torch.full((2, heads, hd, state), 3.0, device=DEV)
+    st = torch.full((2, heads, state, hd), 3.0, device=DEV)
     got, at = [], 0
     for n in (1, 2, 9, 1, 10):                         # slot 1; an unrelated one-token sequence shares every step
         other = torch.randn(1, inner + 2 * gn)
@@ -114,7 +114,7 @@ def test_ssm_scan_carries_state_between_steps(heads, groups, state, hd):
         got.append(y[1:])
         at += n
     _close(torch.cat(got), y_ref.reshape(T, inner), 5e-6)
-    _close(st[1].transpose(1, 2), s_ref, 5e-6)          # kept as [head_dim, state] per head
+    _close(st[1], s_ref, 5e-6)
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 1e-2)])
@@ -204,8 +204,15 @@ def test_sink_attention_portions_and_single_tokens(H, G, D, Dv, softcap, with_si
     _close(out, ref, 1e-5)
 
 
-def test_sink_attention_bf16():
-    out, ref = _attention_case(8, 2, 32, 48, [(7, 0), (1, 40), (12, 70)], 10.0, True, torch.bfloat16)
+@pytest.mark.parametrize("H,G,D,Dv", [(8, 2, 32, 48), (8, 1, 64, 48), (4, 2, 128, 128), (4, 4, 16, 16), (6, 2, 24, 40),
+                                      (2, 1, 72, 104), (3, 3, 20, 12)])
+def test_sink_attention_bf16(H, G, D, Dv):
+    """16-bit activations: the tensor-core tiled kernel where the head sizes allow it (steps of 8 up to 128), the
+    CUDA-core one otherwise; tiles of 64 tokens and 64 keys are crossed with and without a cached prefix."""
+    cases = [(7, 0), (1, 40), (12, 70), (70, 3), (130, 64), (64, 0), (65, 63), (1, 0)]
+    out, ref = _attention_case(H, G, D, Dv, cases, 10.0, True, torch.bfloat16)
+    _close(out, ref, 2e-2)
+    out, ref = _attention_case(H, G, D, Dv, cases[:4], 0.0, False, torch.bfloat16, seed=4)
     _close(out, ref, 2e-2)
 
 
