@@ -235,7 +235,7 @@ def kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) -> list[
         lambda: K.sink_attention(out, qkv, pool, table, p_start, p_ctx, p_slot, None, batch, prompt, sink, H, G, D, D, scale, 30.0),
         flops=att_flops,
         like_fn=lambda: K.flash_attention2_no_pad(q3, k3, v3, scale * 1.4426950408889634, p_start[:batch], lens, prompt))
-    splits = max(1, min(64, -(-(ctx + 1) // 256)))
+    splits = max(1, min(128, -(-(ctx + 1) // 128)))
     per = -(-(-(-(ctx + 1) // splits)) // 32) * 32
     dec_bytes = batch * (ctx + 1) * kvw * es
     seq1 = torch.full((batch,), ctx + 1, dtype=torch.int32, device=dev)

@@ -164,6 +164,13 @@ __global__ void __launch_bounds__(kWarps * 32) sink_attention_kernel(AttnArgs a)
 constexpr int kTileM = 64, kTileN = 64;
 constexpr float kLog2e = 1.4426950408889634f;
 
+// tanh(x) = 1 - 2 / (exp(2x) + 1) on ex2.approx + a fast reciprocal: absolute error ~1e-7, far below the rounding of
+// the 16-bit q and k that feed the score (the fp32 path keeps tanhf)
+__device__ __forceinline__ float tanh_fast(float x) {
+  const float e = fast_exp2(x * (2.0f * kLog2e));
+  return 1.0f - __fdividef(2.0f, e + 1.0f);
+}
+
 template <typename T, int DP, int DVP>
 __global__ void __launch_bounds__(128) sink_attention_mma_kernel(AttnArgs a) {
   pdl_prologue();
@@ -249,7 +256,7 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(AttnArgs a) {
         const int key = k0 + j * 8 + 2 * tq + (e & 1);
         const int lim = (e >> 1) ? pos1 : pos0;
         float v = sc[j][e] * a.scale;
-        if (cap > 0.f) v = cap * tanhf(v * inv_cap);
+        if (cap > 0.f) v = cap * tanh_fast(v * inv_cap);
         v = key <= lim ? v * kLog2e : -INFINITY;
         sc[j][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
@@ -361,6 +368,191 @@ inline bool mma_path_ok(const AttnArgs& a, int dtype) {
   if (a.kv_stride % 8 || a.q_stride % 2 || a.out_stride % 2) return false;
   if (((uintptr_t)a.kv % 16) || ((uintptr_t)a.q % 4) || ((uintptr_t)a.out % 4)) return false;
   return true;
+}
+
+// ---- split mode (decode): one new token per sequence ---------------------------------------------------------------
+// CTA = (key range, kv head x chunk of <= 4 of its query heads, sequence).  Each of the 4 warps walks its own quarter
+// of the range 32 keys at a time: the 32 K rows and V rows are copied raw (T) into the warp's private shared-memory
+// stage with 16-byte loads, lane j scores key j against all the CTA's query heads (so K is read once per kv head, not
+// once per query head), and the value sum runs with lanes over the value columns.  The warps' (max, sum, acc) meet in
+// shared memory, the CTA writes one fp32 partial per (head, range), sink_attention_merge adds the sink.
+constexpr int kSplitRows = 4;
+
+template <typename T, int DVJ>
+__global__ void __launch_bounds__(128) sink_attention_split_kernel(AttnArgs a) {
+  pdl_prologue();
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  const int D = a.D, Dv = a.Dv, per = a.H / a.G;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const int Dp = (D + VEC - 1) / VEC * VEC + VEC, Dvp = (Dv + VEC - 1) / VEC * VEC;       // stage pitches (elements)
+  float* qs = reinterpret_cast<float*>(smem_raw);                        // [kSplitRows][D]
+  float* mrg = qs + kSplitRows * ((D + 3) / 4 * 4);                      // [4 warps][kSplitRows][2 + Dv]
+  T* stage = reinterpret_cast<T*>(mrg + 4 * kSplitRows * (2 + Dv) + ((4 - (4 * kSplitRows * (2 + Dv)) % 4) % 4));
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  T* ks = stage + (size_t)warp * 32 * (Dp + Dvp);
+  T* vs = ks + 32 * Dp;
+  const int z = blockIdx.z, s = a.seq_list ? a.seq_list[z] : z;
+  const int start = a.seq_start[s], ctx = a.seq_ctx[s];
+  const int64_t slot = a.seq_slot[s];
+  const int hchunks = (per + kSplitRows - 1) / kSplitRows;
+  const int g = blockIdx.y / hchunks, h_first = g * per + (blockIdx.y % hchunks) * kSplitRows;
+  const int h_count = min(kSplitRows, g * per + per - h_first);
+  const int key_lo = blockIdx.x * a.chunk, key_hi = min(key_lo + a.chunk, ctx + 1);
+  const T* q = (const T*)a.q;
+  const T* kv = (const T*)a.kv;
+  const int Dq = (D + 3) / 4 * 4;
+  for (int i = tid; i < kSplitRows * Dq; i += 128) {
+    const int r = i / Dq, d = i - r * Dq;
+    qs[i] = (r < h_count && d < D) ? to_f32(q[(int64_t)start * a.q_stride + (h_first + r) * D + d]) : 0.f;
+  }
+  __syncthreads();
+  float m[kSplitRows], l[kSplitRows], acc[kSplitRows][DVJ];
+#pragma unroll
+  for (int r = 0; r < kSplitRows; ++r) {
+    m[r] = -INFINITY; l[r] = 0.f;
+#pragma unroll
+    for (int j = 0; j < DVJ; ++j) acc[r][j] = 0.f;
+  }
+  const int* trow = a.table + slot * a.table_stride;
+  const float inv_cap = a.softcap > 0.f ? 1.0f / a.softcap : 0.f;
+  const bool vec_ok = (D % VEC == 0) && (Dv % VEC == 0) && (a.kv_stride % VEC == 0) && (((uintptr_t)a.kv % 16) == 0);
+  for (int k0 = key_lo + warp * 32; k0 < key_hi; k0 += 128) {
+    const int nk = min(32, key_hi - k0);
+    __syncwarp();
+    if (vec_ok) {
+      const int kc = D / VEC, vc = Dv / VEC;
+      for (int i = lane; i < nk * kc; i += 32) {
+        const int j = i / kc, c = (i - j * kc) * VEC;
+        *reinterpret_cast<uint4*>(ks + j * Dp + c) = ldg_128(kv + (int64_t)trow[k0 + j] * a.kv_stride + g * D + c);
+      }
+      for (int i = lane; i < nk * vc; i += 32) {
+        const int j = i / vc, c = (i - j * vc) * VEC;
+        *reinterpret_cast<uint4*>(vs + j * Dvp + c) = ldg_128(kv + (int64_t)trow[k0 + j] * a.kv_stride + a.G * D + g * Dv + c);
+      }
+    } else {
+      for (int i = lane; i < nk * D; i += 32) {
+        const int j = i / D, d = i - j * D;
+        ks[j * Dp + d] = kv[(int64_t)trow[k0 + j] * a.kv_stride + g * D + d];
+      }
+      for (int i = lane; i < nk * Dv; i += 32) {
+        const int j = i / Dv, d = i - j * Dv;
+        vs[j * Dvp + d] = kv[(int64_t)trow[k0 + j] * a.kv_stride + a.G * D + g * Dv + d];
+      }
+    }
+    __syncwarp();
+    float sc[kSplitRows];
+#pragma unroll
+    for (int r = 0; r < kSplitRows; ++r) sc[r] = 0.f;
+    if (lane < nk) {
+      const T* kr = ks + lane * Dp;
+      if (vec_ok) {                                // 16-byte reads: a quarter warp covers all banks at this pitch
+        for (int d = 0; d < D; d += VEC) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(kr + d);
+          const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+          for (int c = 0; c < VEC; ++c) {
+            const float kvv = to_f32(e[c]);
+#pragma unroll
+            for (int r = 0; r < kSplitRows; ++r) sc[r] = fmaf(qs[r * Dq + d + c], kvv, sc[r]);
+          }
+        }
+      } else {
+        for (int d = 0; d < D; ++d) {
+          const float kvv = to_f32(kr[d]);
+#pragma unroll
+          for (int r = 0; r < kSplitRows; ++r) sc[r] = fmaf(qs[r * Dq + d], kvv, sc[r]);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kSplitRows; ++r) {
+      if (r >= h_count) continue;
+      float sv = sc[r] * a.scale;
+      if (a.softcap > 0.f) sv = a.softcap * tanhf(sv * inv_cap);
+      const bool ok = lane < nk;
+      sv = ok ? sv : -INFINITY;
+      const float mn = fmaxf(m[r], warp_reduce_max(sv));
+      const float corr = expf(m[r] - mn);
+      const float p = ok ? expf(sv - mn) : 0.f;
+      l[r] = l[r] * corr + warp_reduce_sum(p);
+      m[r] = mn;
+#pragma unroll
+      for (int j = 0; j < DVJ; ++j) acc[r][j] *= corr;
+      sc[r] = p;
+    }
+    for (int kk = 0; kk < nk; ++kk) {
+      float vv[DVJ];
+#pragma unroll
+      for (int j = 0; j < DVJ; ++j) {
+        const int d = lane + 32 * j;
+        vv[j] = d < Dv ? to_f32(vs[kk * Dvp + d]) : 0.f;
+      }
+#pragma unroll
+      for (int r = 0; r < kSplitRows; ++r) {
+        const float pk = __shfl_sync(0xffffffffu, sc[r], kk);
+#pragma unroll
+        for (int j = 0; j < DVJ; ++j) acc[r][j] = fmaf(pk, vv[j], acc[r][j]);
+      }
+    }
+  }
+  // the four warps' partials meet in shared memory; warp w finishes row w
+#pragma unroll
+  for (int r = 0; r < kSplitRows; ++r) {
+    float* dst = mrg + (warp * kSplitRows + r) * (2 + Dv);
+    if (lane == 0) { dst[0] = m[r]; dst[1] = l[r]; }
+#pragma unroll
+    for (int j = 0; j < DVJ; ++j) {
+      const int d = lane + 32 * j;
+      if (d < Dv) dst[2 + d] = acc[r][j];
+    }
+  }
+  __syncthreads();
+  if (warp < h_count) {
+    const int r = warp;
+    float mf = -INFINITY;
+    for (int w = 0; w < 4; ++w) mf = fmaxf(mf, mrg[(w * kSplitRows + r) * (2 + Dv)]);
+    float den = 0.f, sc4[4];
+    for (int w = 0; w < 4; ++w) {
+      const float mw = mrg[(w * kSplitRows + r) * (2 + Dv)];
+      sc4[w] = mw == -INFINITY ? 0.f : expf(mw - mf);
+      den += mrg[(w * kSplitRows + r) * (2 + Dv) + 1] * sc4[w];
+    }
+    float* dst = a.part + (((int64_t)z * a.H + h_first + r) * a.nsplit + blockIdx.x) * (Dv + 2);
+    if (lane == 0) { dst[0] = mf; dst[1] = den; }
+    for (int d = lane; d < Dv; d += 32) {
+      float v = 0.f;
+      for (int w = 0; w < 4; ++w) v = fmaf(mrg[(w * kSplitRows + r) * (2 + Dv) + 2 + d], sc4[w], v);
+      dst[2 + d] = v;
+    }
+  }
+}
+
+template <typename T>
+int launch_attention_split(const AttnArgs& a, int64_t num_seqs, cudaStream_t st) {
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const int Dp = (a.D + VEC - 1) / VEC * VEC + VEC, Dvp = (a.Dv + VEC - 1) / VEC * VEC;
+  const int Dq = (a.D + 3) / 4 * 4;
+  int mfl = 4 * kSplitRows * (2 + a.Dv);
+  mfl += (4 - mfl % 4) % 4;
+  const size_t smem = (size_t)(kSplitRows * Dq + mfl) * sizeof(float) + (size_t)4 * 32 * (Dp + Dvp) * sizeof(T);
+  B2L_REQUIRE((int64_t)smem <= b2l_max_smem_optin(), "sink_attention: head sizes %d / %d need %lld bytes of shared memory",
+              a.D, a.Dv, (long long)smem);
+  const int dvj = (a.Dv + 31) / 32;
+  B2L_REQUIRE(dvj <= 8, "sink_attention: value head size %d > 256", a.Dv);
+  const int per = a.H / a.G, hchunks = (per + kSplitRows - 1) / kSplitRows;
+  const dim3 grid((unsigned)a.nsplit, (unsigned)(a.G * hchunks), (unsigned)num_seqs);
+#define B2L_SPLIT(J)                                                                                     \
+  do {                                                                                                   \
+    static int cache[64] = {0};                                                                          \
+    B2L_CUDA_CHECK(b2l_ensure_dynamic_smem(sink_attention_split_kernel<T, J>, (int)smem, cache));        \
+    b2l_launch(sink_attention_split_kernel<T, J>, grid, dim3(128), smem, st, a);                         \
+  } while (0)
+  if (dvj <= 2) B2L_SPLIT(2);
+  else if (dvj <= 4) B2L_SPLIT(4);
+  else B2L_SPLIT(8);
+#undef B2L_SPLIT
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
 }
 
 template <typename T>
@@ -519,7 +711,7 @@ extern "C" int b2l_sink_attention(void* out, int64_t out_row_stride, const void*
     a.PH = per < kRows ? per : kRows;
     const dim3 grid((unsigned)num_splits, (unsigned)(kv_heads * hchunks), (unsigned)num_seqs);
     int rc = B2L_OK;
-    B2L_DISPATCH_FLOAT(dtype, "sink_attention", { rc = launch_attention<T, true>(a, grid, st); });
+    B2L_DISPATCH_FLOAT(dtype, "sink_attention", { rc = launch_attention_split<T>(a, num_seqs, st); });
     if (rc != B2L_OK) return rc;
     B2L_DISPATCH_FLOAT(dtype, "sink_attention", {
       b2l_launch(sink_attention_merge_kernel<T>, dim3((unsigned)heads, (unsigned)num_seqs), dim3(64), (size_t)0, st,

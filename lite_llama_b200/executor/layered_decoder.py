@@ -93,8 +93,8 @@ def mamba2_mixer(li: int, spec: Mamba2Spec, w: dict[str, torch.Tensor], x: torch
     return linear(gated, w["o"])
 
 
-_SPLIT_KEYS = 256          # keys per CTA of the single-token attention kernel
-_MAX_SPLITS = 64
+_SPLIT_KEYS = 128          # keys per CTA of the single-token attention kernel (4 warps x 32 keys per pass)
+_MAX_SPLITS = 128
 
 
 def sink_attention_mixer(li: int, spec: SinkAttentionSpec, w: dict[str, torch.Tensor], x: torch.Tensor,
