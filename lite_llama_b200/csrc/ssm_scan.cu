@@ -78,12 +78,14 @@ __global__ void conv_tail_update_kernel(T* __restrict__ tail, const T* __restric
 // the rows are cut into `nslices` warps whose partial sums meet in shared memory once per chunk of kChunk tokens
 // (fixed slice order: deterministic).  The scan of one sequence is serial, so latency decides: kLoadWarps extra warps
 // stage the NEXT chunk's B_t, C_t, x_t (as fp32) and dt / decay into the other half of a double buffer while the
-// compute warps run the current one; the compute warps read them as broadcast float4.
+// compute warps run the current one; the compute warps read them as broadcast float4, and with CPL = 2 every value
+// read serves two columns per lane (shared-memory bandwidth, not the FMA pipe, bounds the token loop).
 // State layout: [slot, head, n, p] (p contiguous = coalesced per n).
 constexpr int kChunk = 16;
 constexpr int kLoadWarps = 4;
+constexpr int kVecBatch = 4;
 
-template <typename T, int NPT>
+template <typename T, int NPT, int CPL>
 __global__ void __launch_bounds__(512) ssm_scan_kernel(
     float* __restrict__ y, float* __restrict__ state, const T* __restrict__ xbc, int64_t xbc_stride,
     const T* __restrict__ dt_raw, int64_t dt_stride, const T* __restrict__ dt_bias, const T* __restrict__ a_log,
@@ -91,7 +93,7 @@ __global__ void __launch_bounds__(512) ssm_scan_kernel(
     const int* __restrict__ seq_slot, int heads, int groups, int N, int P, int ctiles, int nslices) {
   pdl_prologue();
   extern __shared__ __align__(16) float sm[];
-  const int Np = nslices * NPT, cols = ctiles * 32;
+  const int Np = nslices * NPT, cols = ctiles * 32 * CPL;
   const int stage_floats = 2 * kChunk * Np + kChunk * cols + 2 * kChunk;
   float* sYbase = sm + 2 * stage_floats;       // [2][nslices][kChunk][cols], nslices > 1 only
   const int s = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * cols;
@@ -99,7 +101,8 @@ __global__ void __launch_bounds__(512) ssm_scan_kernel(
   const int cwarps = ctiles * nslices;
   const bool computes = warp < cwarps;
   const int ct = warp / nslices, sl = warp - ct * nslices;
-  const int col = col0 + ct * 32 + lane, n0 = sl * NPT;
+  const int wcol = ct * 32 * CPL + lane;                   // this lane's first column inside the CTA's tile
+  const int col = col0 + wcol, n0 = sl * NPT;              // its columns: col + 32 j, j < CPL
   const int start = seq_start[s], len = seq_start[s + 1] - start, ctx = seq_ctx[s];
   if (len <= 0) return;
   const int64_t slot = seq_slot[s];
@@ -108,6 +111,9 @@ __global__ void __launch_bounds__(512) ssm_scan_kernel(
   const int boff = inner + g * N, coff = inner + groups * N + g * N;
   const int nchunks = (len + kChunk - 1) / kChunk;
 
+  constexpr int VEC = 16 / (int)sizeof(T);
+  // whole 16-byte vectors line up when every column offset and the row stride are multiples of VEC elements
+  const bool vec_ok = (N % VEC == 0) && (P % VEC == 0) && (xbc_stride % VEC == 0) && (((uintptr_t)xbc % 16) == 0);
   // stage chunk k into half k & 1 with `nth` threads numbered `t0`
   auto stage = [&](int k, int t0, int nth) {
     float* sB = sm + (k & 1) * stage_floats;
@@ -116,19 +122,70 @@ __global__ void __launch_bounds__(512) ssm_scan_kernel(
     float* sDt = sX + kChunk * cols;
     const int c0 = k * kChunk, tc = min(kChunk, len - c0);
     const T* rows = xbc + (int64_t)(start + c0) * xbc_stride;
+    if (vec_ok) {
+      // 16-byte loads, kVecBatch of them in flight per thread before the first shared-memory store
+      const int nv = Np / VEC, per_op = tc * nv;
+      for (int base = t0; base < 2 * per_op; base += nth * kVecBatch) {
+        uint4 raw[kVecBatch];
+#pragma unroll
+        for (int u = 0; u < kVecBatch; ++u) {
+          const int idx = base + u * nth;
+          raw[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (idx < 2 * per_op) {
+            const int op = idx >= per_op, rem = idx - op * per_op, t = rem / nv, n = (rem - t * nv) * VEC;
+            if (n < N) raw[u] = ldg_128(rows + (int64_t)t * xbc_stride + (op ? coff : boff) + n);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kVecBatch; ++u) {
+          const int idx = base + u * nth;
+          if (idx < 2 * per_op) {
+            const int op = idx >= per_op, rem = idx - op * per_op, t = rem / nv, n = (rem - t * nv) * VEC;
+            float* dst = (op ? sC : sB) + t * Np + n;
+            const T* e = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+            for (int c = 0; c < VEC; ++c) dst[c] = to_f32(e[c]);
+          }
+        }
+      }
+      const int xv = cols / VEC;
+      for (int base = t0; base < tc * xv; base += nth * kVecBatch) {
+        uint4 raw[kVecBatch];
+#pragma unroll
+        for (int u = 0; u < kVecBatch; ++u) {
+          const int idx = base + u * nth;
+          raw[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (idx < tc * xv) {
+            const int t = idx / xv, c = (idx - t * xv) * VEC;
+            if (col0 + c < P) raw[u] = ldg_128(rows + (int64_t)t * xbc_stride + h * P + col0 + c);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kVecBatch; ++u) {
+          const int idx = base + u * nth;
+          if (idx < tc * xv) {
+            const int t = idx / xv, c = (idx - t * xv) * VEC;
+            const T* e = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+            for (int k2 = 0; k2 < VEC; ++k2) sX[t * cols + c + k2] = to_f32(e[k2]);
+          }
+        }
+      }
+    } else {
 #pragma unroll 8
-    for (int i = t0; i < tc * Np; i += nth) {
-      const int t = i / Np, n = i - t * Np;
-      const T* r = rows + (int64_t)t * xbc_stride;
-      const float bv = n < N ? to_f32(r[boff + n]) : 0.f;
-      const float cv = n < N ? to_f32(r[coff + n]) : 0.f;
-      sB[i] = bv;
-      sC[i] = cv;
-    }
+      for (int i = t0; i < tc * Np; i += nth) {
+        const int t = i / Np, n = i - t * Np;
+        const T* r = rows + (int64_t)t * xbc_stride;
+        const float bv = n < N ? to_f32(r[boff + n]) : 0.f;
+        const float cv = n < N ? to_f32(r[coff + n]) : 0.f;
+        sB[i] = bv;
+        sC[i] = cv;
+      }
 #pragma unroll 8
-    for (int i = t0; i < tc * cols; i += nth) {
-      const int t = i / cols, c = i - t * cols;
-      sX[i] = (col0 + c < P) ? to_f32(rows[(int64_t)t * xbc_stride + h * P + col0 + c]) : 0.f;
+      for (int i = t0; i < tc * cols; i += nth) {
+        const int t = i / cols, c = i - t * cols;
+        sX[i] = (col0 + c < P) ? to_f32(rows[(int64_t)t * xbc_stride + h * P + col0 + c]) : 0.f;
+      }
     }
     if (t0 < tc) {
       const float dtv = softplus_f(to_f32(dt_raw[(int64_t)(start + c0 + t0) * dt_stride + h]) + bias);
@@ -151,10 +208,16 @@ __global__ void __launch_bounds__(512) ssm_scan_kernel(
   };
 
   float* st = state + ((slot * heads + h) * (int64_t)N) * P;            // [N, P]
-  float S[NPT];
+  float2 S[CPL][NPT / 2];                                               // rows n0 + 2i, n0 + 2i + 1 of column j
   if (computes) {
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) S[i] = (ctx > 0 && n0 + i < N && col < P) ? st[(int64_t)(n0 + i) * P + col] : 0.f;
+    for (int j = 0; j < CPL; ++j)
+#pragma unroll
+      for (int i = 0; i < NPT / 2; ++i) {
+        const bool live = ctx > 0 && col + 32 * j < P;
+        S[j][i].x = (live && n0 + 2 * i < N) ? st[(int64_t)(n0 + 2 * i) * P + col + 32 * j] : 0.f;
+        S[j][i].y = (live && n0 + 2 * i + 1 < N) ? st[(int64_t)(n0 + 2 * i + 1) * P + col + 32 * j] : 0.f;
+      }
   }
   stage(0, tid, blockDim.x);
   __syncthreads();
@@ -167,24 +230,39 @@ __global__ void __launch_bounds__(512) ssm_scan_kernel(
       float* sY = sYbase + (k & 1) * nslices * kChunk * cols;
       const int c0 = k * kChunk, tc = min(kChunk, len - c0);
       for (int t = 0; t < tc; ++t) {
-        const float dtv = sDt[t], dec = sDt[kChunk + t], xv = sX[t * cols + ct * 32 + lane];
-        const float dx = dtv * xv;
+        const float dtv = sDt[t], dec = sDt[kChunk + t];
+        float xv[CPL];
+        float2 dx2[CPL], acc0[CPL], acc1[CPL];
+#pragma unroll
+        for (int j = 0; j < CPL; ++j) {
+          xv[j] = sX[t * cols + wcol + 32 * j];
+          dx2[j] = make_float2(dtv * xv[j], dtv * xv[j]);
+          acc0[j] = acc1[j] = make_float2(0.f, 0.f);
+        }
         const float4* b4 = reinterpret_cast<const float4*>(sB + t * Np + n0);
         const float4* c4 = reinterpret_cast<const float4*>(sC + t * Np + n0);
-        float acc0 = 0.f, acc1 = 0.f;
+        // packed fp32 (two state rows per instruction): S <- dec * S + dx * b;  acc += S * c
+        // every B / C value read from shared memory serves CPL columns
+        const float2 dec2 = make_float2(dec, dec);
 #pragma unroll
         for (int i = 0; i < NPT / 4; ++i) {
           const float4 b = b4[i], c = c4[i];
-          S[4 * i + 0] = fmaf(dec, S[4 * i + 0], dx * b.x); acc0 = fmaf(S[4 * i + 0], c.x, acc0);
-          S[4 * i + 1] = fmaf(dec, S[4 * i + 1], dx * b.y); acc1 = fmaf(S[4 * i + 1], c.y, acc1);
-          S[4 * i + 2] = fmaf(dec, S[4 * i + 2], dx * b.z); acc0 = fmaf(S[4 * i + 2], c.z, acc0);
-          S[4 * i + 3] = fmaf(dec, S[4 * i + 3], dx * b.w); acc1 = fmaf(S[4 * i + 3], c.w, acc1);
+#pragma unroll
+          for (int j = 0; j < CPL; ++j) {
+            S[j][2 * i] = __ffma2_rn(dec2, S[j][2 * i], __fmul2_rn(dx2[j], make_float2(b.x, b.y)));
+            acc0[j] = __ffma2_rn(S[j][2 * i], make_float2(c.x, c.y), acc0[j]);
+            S[j][2 * i + 1] = __ffma2_rn(dec2, S[j][2 * i + 1], __fmul2_rn(dx2[j], make_float2(b.z, b.w)));
+            acc1[j] = __ffma2_rn(S[j][2 * i + 1], make_float2(c.z, c.w), acc1[j]);
+          }
         }
-        const float acc = acc0 + acc1;
-        if (nslices == 1) {
-          if (col < P) y[(int64_t)(start + c0 + t) * inner + h * P + col] = fmaf(dsk, xv, acc);
-        } else {
-          sY[(sl * kChunk + t) * cols + ct * 32 + lane] = acc;
+#pragma unroll
+        for (int j = 0; j < CPL; ++j) {
+          const float acc = (acc0[j].x + acc0[j].y) + (acc1[j].x + acc1[j].y);
+          if (nslices == 1) {
+            if (col + 32 * j < P) y[(int64_t)(start + c0 + t) * inner + h * P + col + 32 * j] = fmaf(dsk, xv[j], acc);
+          } else {
+            sY[(sl * kChunk + t) * cols + wcol + 32 * j] = acc;
+          }
         }
       }
     } else {
@@ -200,12 +278,18 @@ __global__ void __launch_bounds__(512) ssm_scan_kernel(
   if (nslices > 1) reduce(nchunks - 1, tid, blockDim.x);
   if (computes) {
 #pragma unroll
-    for (int i = 0; i < NPT; ++i)
-      if (n0 + i < N && col < P) st[(int64_t)(n0 + i) * P + col] = S[i];
+    for (int j = 0; j < CPL; ++j)
+#pragma unroll
+      for (int i = 0; i < NPT / 2; ++i) {
+        if (n0 + 2 * i < N && col + 32 * j < P) st[(int64_t)(n0 + 2 * i) * P + col + 32 * j] = S[j][i].x;
+        if (n0 + 2 * i + 1 < N && col + 32 * j < P) st[(int64_t)(n0 + 2 * i + 1) * P + col + 32 * j] = S[j][i].y;
+      }
   }
 }
 
-template <typename T>
+// One CTA per (group, token).  VPT > 0: the gated values of the group fit in VPT registers per thread, so y and z are
+// read once; VPT == 0: any group size, the gate is recomputed in the second pass.
+template <typename T, int VPT>
 __global__ void gated_group_norm_kernel(T* __restrict__ o, const float* __restrict__ y, const T* __restrict__ z,
                                         int64_t z_stride, const T* __restrict__ w, int inner, int groups, float eps) {
   pdl_prologue();
@@ -213,9 +297,19 @@ __global__ void gated_group_norm_kernel(T* __restrict__ o, const float* __restri
   const int64_t t = blockIdx.y;
   const int gs = inner / groups, base = blockIdx.x * gs;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < gs; i += blockDim.x) {
-    const float v = y[t * inner + base + i] * silu_f(to_f32(z[t * z_stride + base + i]));
-    ss = fmaf(v, v, ss);
+  float keep[VPT > 0 ? VPT : 1];
+  if (VPT > 0) {
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      keep[k] = i < gs ? y[t * inner + base + i] * silu_f(to_f32(z[t * z_stride + base + i])) : 0.f;
+      ss = fmaf(keep[k], keep[k], ss);
+    }
+  } else {
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+      const float v = y[t * inner + base + i] * silu_f(to_f32(z[t * z_stride + base + i]));
+      ss = fmaf(v, v, ss);
+    }
   }
   ss = warp_reduce_sum(ss);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -224,9 +318,17 @@ __global__ void gated_group_norm_kernel(T* __restrict__ o, const float* __restri
   float tot = lane < nw ? red[lane] : 0.f;
   tot = warp_reduce_sum(tot);
   const float rr = 1.0f / sqrtf(tot / (float)gs + eps);
-  for (int i = threadIdx.x; i < gs; i += blockDim.x) {
-    const float v = y[t * inner + base + i] * silu_f(to_f32(z[t * z_stride + base + i]));
-    o[t * inner + base + i] = from_f32<T>(v * rr * to_f32(w[base + i]));
+  if (VPT > 0) {
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      if (i < gs) o[t * inner + base + i] = from_f32<T>(keep[k] * rr * to_f32(w[base + i]));
+    }
+  } else {
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+      const float v = y[t * inner + base + i] * silu_f(to_f32(z[t * z_stride + base + i]));
+      o[t * inner + base + i] = from_f32<T>(v * rr * to_f32(w[base + i]));
+    }
   }
 }
 
@@ -266,31 +368,38 @@ extern "C" int b2l_ssm_scan(void* y_f32, void* state_f32, const void* xbc, int64
   B2L_REQUIRE(state_size <= 768, "ssm_scan: state size %d > 768", state_size);
   if (num_seqs <= 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  const int npt = state_size <= 16 ? 16 : (state_size <= 32 ? 32 : 64);
+  // two columns per lane when the head is wider than a warp and the state rows still fit 12 compute warps
+  const int cpl = (head_dim > 32 && state_size <= 384) ? 2 : 1;
+  const int npt = state_size <= 16 ? 16 : ((state_size <= 32 || cpl == 2) ? 32 : 64);
   const int nslices = (state_size + npt - 1) / npt;
-  int ctiles = (head_dim + 31) / 32;
+  int ctiles = (head_dim + 32 * cpl - 1) / (32 * cpl);
   const int room = 8 / nslices > 1 ? 8 / nslices : 1;      // compute warps <= 12 with the 4 loaders: <= 512 threads
   if (ctiles > room) ctiles = room;
-  const int cols = ctiles * 32, np = nslices * npt;
+  const int cols = ctiles * 32 * cpl, np = nslices * npt;
   const size_t smem = (size_t)(2 * (2 * kChunk * np + kChunk * cols + 2 * kChunk) +
                                (nslices > 1 ? 2 * nslices * kChunk * cols : 0)) * sizeof(float);
   B2L_REQUIRE((int64_t)smem <= b2l_max_smem_optin(), "ssm_scan: state size %d needs %lld bytes of shared memory",
               state_size, (long long)smem);
   const dim3 block((ctiles * nslices + kLoadWarps) * 32), grid((unsigned)cdiv64(head_dim, cols), (unsigned)heads,
                                                                (unsigned)num_seqs);
-#define B2L_SCAN(NPTV)                                                                                               \
+#define B2L_SCAN(NPTV, CPLV)                                                                                         \
   do {                                                                                                               \
     static int cache[64] = {0};                                                                                      \
-    B2L_CUDA_CHECK(b2l_ensure_dynamic_smem(ssm_scan_kernel<T, NPTV>, (int)smem, cache));                             \
-    b2l_launch(ssm_scan_kernel<T, NPTV>, grid, block, smem, st, (float*)y_f32, (float*)state_f32, (const T*)xbc,     \
-               xbc_row_stride, (const T*)dt_raw, dt_row_stride, (const T*)dt_bias, (const T*)a_log,                  \
+    B2L_CUDA_CHECK(b2l_ensure_dynamic_smem(ssm_scan_kernel<T, NPTV, CPLV>, (int)smem, cache));                       \
+    b2l_launch(ssm_scan_kernel<T, NPTV, CPLV>, grid, block, smem, st, (float*)y_f32, (float*)state_f32,              \
+               (const T*)xbc, xbc_row_stride, (const T*)dt_raw, dt_row_stride, (const T*)dt_bias, (const T*)a_log,   \
                (const T*)d_skip, (const int*)seq_start, (const int*)seq_ctx, (const int*)seq_slot, heads, groups,    \
                state_size, head_dim, ctiles, nslices);                                                               \
   } while (0)
   B2L_DISPATCH_FLOAT(dtype, "ssm_scan", {
-    if (npt == 16) B2L_SCAN(16);
-    else if (npt == 32) B2L_SCAN(32);
-    else B2L_SCAN(64);
+    if (cpl == 2) {
+      if (npt == 16) B2L_SCAN(16, 2);
+      else B2L_SCAN(32, 2);
+    } else {
+      if (npt == 16) B2L_SCAN(16, 1);
+      else if (npt == 32) B2L_SCAN(32, 1);
+      else B2L_SCAN(64, 1);
+    }
   });
 #undef B2L_SCAN
   B2L_LAUNCH_CHECK();
@@ -306,10 +415,18 @@ extern "C" int b2l_gated_group_norm(void* out, const void* y_f32, const void* z,
   cudaStream_t st = (cudaStream_t)stream;
   const int gs = inner / groups;
   const int threads = gs >= 1024 ? 256 : (gs >= 256 ? 128 : (gs >= 64 ? 64 : 32));
+  const int vpt = (gs + threads - 1) / threads;
+#define B2L_GGN(V)                                                                                                  \
+  b2l_launch(gated_group_norm_kernel<T, V>, dim3((unsigned)groups, (unsigned)rows), dim3(threads), (size_t)0, st,  \
+             (T*)out, (const float*)y_f32, (const T*)z, z_row_stride, (const T*)weight, inner, groups, eps)
   B2L_DISPATCH_FLOAT(dtype, "gated_group_norm", {
-    b2l_launch(gated_group_norm_kernel<T>, dim3((unsigned)groups, (unsigned)rows), dim3(threads), (size_t)0, st, (T*)out,
-               (const float*)y_f32, (const T*)z, z_row_stride, (const T*)weight, inner, groups, eps);
+    if (vpt <= 1) B2L_GGN(1);
+    else if (vpt <= 2) B2L_GGN(2);
+    else if (vpt <= 4) B2L_GGN(4);
+    else if (vpt <= 8) B2L_GGN(8);
+    else B2L_GGN(0);
   });
+#undef B2L_GGN
   B2L_LAUNCH_CHECK();
   return B2L_OK;
 }

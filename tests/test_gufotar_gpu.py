@@ -91,7 +91,8 @@ def test_causal_conv_with_tail_over_portions(taps):
 
 
 @pytest.mark.parametrize("heads,groups,state,hd", [(4, 2, 12, 6), (3, 1, 48, 7), (2, 2, 100, 16), (2, 1, 130, 4),
-                                                   (1, 1, 1, 1)])
+                                                   (1, 1, 1, 1), (2, 1, 40, 70), (2, 2, 130, 40), (1, 1, 400, 33),
+                                                   (2, 1, 16, 64)])
 def test_ssm_scan_carries_state_between_steps(heads, groups, state, hd):
     from lite_llama_b200.kernels import ssm_scan
 
