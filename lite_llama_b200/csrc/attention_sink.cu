@@ -157,7 +157,8 @@ __global__ void __launch_bounds__(kWarps * 32) sink_attention_kernel(AttnArgs a)
 // ---- tiled mode on the tensor cores (16-bit T) ------------------------------------------------------------------
 // CTA = 64 new tokens of one (sequence, query head); 4 warps x 16 query rows (FlashAttention-2 schedule, the same
 // fragment handling as flash_attention_nopad.cu).  64-key K and V tiles are gathered through the request table with
-// 16-byte loads into padded shared memory (head sizes are padded to DP / DVP columns of zeros), S = Q K^T and
+// 16-byte asynchronous copies into a two-stage padded shared-memory ring (head sizes are padded to DP / DVP columns
+// of zeros; the next tile's copies fly while the current one is multiplied), S = Q K^T and
 // O += P V run on mma.sync m16n8k16 with fp32 accumulators, the soft cap is applied to the fp32 scores, the online
 // softmax works in the log2 domain, the sink joins the denominator once at the end.  Keys 0 .. ctx + t (cached prefix
 // + the portion itself) are visible to token t.  Needs D, Dv multiples of 8 and <= 128, 16-byte aligned pool rows.
@@ -171,13 +172,19 @@ __device__ __forceinline__ float tanh_fast(float x) {
   return 1.0f - __fdividef(2.0f, e + 1.0f);
 }
 
+// 16-byte asynchronous global -> shared copies (the gathered rows have no tensor-map shape, so no TMA tile)
+__device__ __forceinline__ void cp_async_16(uint32_t saddr, const void* g) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(g) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <typename T, int DP, int DVP>
 __global__ void __launch_bounds__(128) sink_attention_mma_kernel(AttnArgs a) {
   pdl_prologue();
   extern __shared__ __align__(16) uint8_t smem_raw[];
   constexpr int KP = (DP + 8) * 2, VP = (DVP + 8) * 2;          // row pitches in bytes
-  uint8_t* ks_ptr = smem_raw;
-  uint8_t* vs_ptr = smem_raw + kTileN * KP;
+  constexpr int kStage = kTileN * (KP + VP);                    // one K tile + one V tile; two stages
   const int D = a.D, Dv = a.Dv, per = a.H / a.G;
   const int z = blockIdx.z, s = a.seq_list ? a.seq_list[z] : z;
   const int start = a.seq_start[s], qlen = a.seq_start[s + 1] - start, ctx = a.seq_ctx[s];
@@ -214,23 +221,36 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(AttnArgs a) {
   const int warp_last = ctx + t0 + warp * 16 + 15;
   const int* trow = a.table + slot * a.table_stride;
   const float cap = a.softcap, inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
-  const uint32_t ks = smem_u32(ks_ptr), vs = smem_u32(vs_ptr);
-  for (int k0 = 0; k0 < key_hi; k0 += kTileN) {
-    __syncthreads();
+  // tile k0 -> stage `st`: asynchronous 16-byte copies of the rows the table names; rows / columns past the end are
+  // zero-filled with plain stores (disjoint addresses)
+  auto issue = [&](int k0, int st) {
+    uint8_t* kdst = smem_raw + st * kStage;
+    uint8_t* vdst = kdst + kTileN * KP;
     for (int i = tid; i < kTileN * (DP / 8); i += 128) {
       const int r = i / (DP / 8), c = (i - r * (DP / 8)) * 8;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (k0 + r < key_hi && c < D) v = ldg_128(kv + (int64_t)trow[k0 + r] * a.kv_stride + g * D + c);
-      *reinterpret_cast<uint4*>(ks_ptr + r * KP + c * 2) = v;
+      if (k0 + r < key_hi && c < D)
+        cp_async_16(smem_u32(kdst + r * KP + c * 2), kv + (int64_t)trow[k0 + r] * a.kv_stride + g * D + c);
+      else
+        *reinterpret_cast<uint4*>(kdst + r * KP + c * 2) = make_uint4(0u, 0u, 0u, 0u);
     }
     for (int i = tid; i < kTileN * (DVP / 8); i += 128) {
       const int r = i / (DVP / 8), c = (i - r * (DVP / 8)) * 8;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (k0 + r < key_hi && c < Dv) v = ldg_128(kv + (int64_t)trow[k0 + r] * a.kv_stride + a.G * D + g * Dv + c);
-      *reinterpret_cast<uint4*>(vs_ptr + r * VP + c * 2) = v;
+      if (k0 + r < key_hi && c < Dv)
+        cp_async_16(smem_u32(vdst + r * VP + c * 2), kv + (int64_t)trow[k0 + r] * a.kv_stride + a.G * D + g * Dv + c);
+      else
+        *reinterpret_cast<uint4*>(vdst + r * VP + c * 2) = make_uint4(0u, 0u, 0u, 0u);
     }
-    __syncthreads();
-    if (k0 > warp_last) continue;                                // warp-uniform: the tile is above this warp's rows
+    cp_async_commit();
+  };
+  issue(0, 0);
+  for (int k0 = 0, it = 0; k0 < key_hi; k0 += kTileN, ++it) {
+    const bool more = k0 + kTileN < key_hi;
+    if (more) issue(k0 + kTileN, (it + 1) & 1);                  // the next tile flies while this one is used
+    if (more) cp_async_wait<1>(); else cp_async_wait<0>();
+    __syncthreads();                                             // tile `it` is complete and visible to every warp
+    const uint32_t ks = smem_u32(smem_raw + (it & 1) * kStage), vs = ks + kTileN * KP;
+    // the barrier at the END of the body keeps stage it & 1 intact until every warp is done with it
+    if (k0 > warp_last) { __syncthreads(); continue; }
     float sc[kTileN / 8][4];
 #pragma unroll
     for (int j = 0; j < kTileN / 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
@@ -308,6 +328,7 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(AttnArgs a) {
         }
       }
     }
+    __syncthreads();
   }
   float inv[2];
 #pragma unroll
@@ -340,7 +361,7 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(AttnArgs a) {
 
 template <typename T, int DP, int DVP>
 int launch_attention_mma(const AttnArgs& a, int max_q_len, int64_t num_seqs, cudaStream_t st) {
-  constexpr int smem = kTileN * ((DP + 8) * 2 + (DVP + 8) * 2);
+  constexpr int smem = 2 * kTileN * ((DP + 8) * 2 + (DVP + 8) * 2);      // two stages
   static int cache[64] = {0};
   B2L_CUDA_CHECK(b2l_ensure_dynamic_smem(sink_attention_mma_kernel<T, DP, DVP>, smem, cache));
   const dim3 grid((unsigned)((max_q_len + kTileM - 1) / kTileM), (unsigned)a.H, (unsigned)num_seqs);
@@ -377,6 +398,7 @@ inline bool mma_path_ok(const AttnArgs& a, int dtype) {
 // once per query head), and the value sum runs with lanes over the value columns.  The warps' (max, sum, acc) meet in
 // shared memory, the CTA writes one fp32 partial per (head, range), sink_attention_merge adds the sink.
 constexpr int kSplitRows = 4;
+constexpr int kStageBatch = 8;
 
 template <typename T, int DVJ>
 __global__ void __launch_bounds__(128) sink_attention_split_kernel(AttnArgs a) {
@@ -420,15 +442,28 @@ __global__ void __launch_bounds__(128) sink_attention_split_kernel(AttnArgs a) {
     const int nk = min(32, key_hi - k0);
     __syncwarp();
     if (vec_ok) {
-      const int kc = D / VEC, vc = Dv / VEC;
-      for (int i = lane; i < nk * kc; i += 32) {
-        const int j = i / kc, c = (i - j * kc) * VEC;
-        *reinterpret_cast<uint4*>(ks + j * Dp + c) = ldg_128(kv + (int64_t)trow[k0 + j] * a.kv_stride + g * D + c);
-      }
-      for (int i = lane; i < nk * vc; i += 32) {
-        const int j = i / vc, c = (i - j * vc) * VEC;
-        *reinterpret_cast<uint4*>(vs + j * Dvp + c) = ldg_128(kv + (int64_t)trow[k0 + j] * a.kv_stride + a.G * D + g * Dv + c);
-      }
+      // lane j fetches key j's pool row once; the 16-byte copies run in batches of kStageBatch loads per lane that
+      // are all in flight before the first shared-memory store
+      const int my_row = lane < nk ? trow[k0 + lane] : 0;
+      auto stage_rows = [&](T* dst, int pitch, int col0, int vecs) {
+        for (int base = 0; base < nk * vecs; base += 32 * kStageBatch) {
+          uint4 raw[kStageBatch];
+#pragma unroll
+          for (int u = 0; u < kStageBatch; ++u) {
+            const int idx = base + u * 32 + lane, j = min(idx / vecs, 31), c = (idx - (idx / vecs) * vecs) * VEC;
+            const int row = __shfl_sync(0xffffffffu, my_row, j);
+            raw[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (idx < nk * vecs) raw[u] = ldg_128(kv + (int64_t)row * a.kv_stride + col0 + c);
+          }
+#pragma unroll
+          for (int u = 0; u < kStageBatch; ++u) {
+            const int idx = base + u * 32 + lane, j = idx / vecs, c = (idx - j * vecs) * VEC;
+            if (idx < nk * vecs) *reinterpret_cast<uint4*>(dst + j * pitch + c) = raw[u];
+          }
+        }
+      };
+      stage_rows(ks, Dp, g * D, D / VEC);
+      stage_rows(vs, Dvp, a.G * D + g * Dv, Dv / VEC);
     } else {
       for (int i = lane; i < nk * D; i += 32) {
         const int j = i / D, d = i - j * D;

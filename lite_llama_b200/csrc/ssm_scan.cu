@@ -51,6 +51,45 @@ __global__ void causal_conv_silu_kernel(T* __restrict__ out, const T* __restrict
   out[(int64_t)tok * channels + c] = from_f32<T>(silu_f(acc));
 }
 
+// The same with 16-byte accesses: one thread = VEC consecutive channels (channels, the input row stride and the
+// column window's start all multiples of VEC elements).
+template <typename T>
+__global__ void causal_conv_silu_vec_kernel(T* __restrict__ out, const T* __restrict__ in, int64_t in_stride,
+                                            const T* __restrict__ w, const T* __restrict__ bias,
+                                            const T* __restrict__ tail, const int* __restrict__ seq_start,
+                                            const int* __restrict__ seq_ctx, const int* __restrict__ seq_slot,
+                                            int nseq, int channels, int taps) {
+  pdl_prologue();
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const int tok = blockIdx.y;
+  const int s = find_seq(seq_start, nseq, tok);
+  const int local = tok - seq_start[s], ctx = seq_ctx[s];
+  const int64_t slot = seq_slot[s];
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+  if (c >= channels) return;
+  float acc[VEC];
+  {
+    const uint4 raw = ldg_128(bias + c);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) acc[k] = to_f32(e[k]);
+  }
+  for (int j = 0; j < taps; ++j) {
+    const int i = local - j;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (i >= 0) raw = ldg_128(in + (int64_t)(tok - j) * in_stride + c);
+    else if (ctx + i >= 0) raw = ldg_128(tail + (slot * (taps - 1) + (taps - 1 + i)) * channels + c);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) acc[k] = fmaf(to_f32(w[(int64_t)(c + k) * taps + (taps - 1 - j)]), to_f32(e[k]), acc[k]);
+  }
+  uint4 res;
+  T* e = reinterpret_cast<T*>(&res);
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) e[k] = from_f32<T>(silu_f(acc[k]));
+  *reinterpret_cast<uint4*>(out + (int64_t)tok * channels + c) = res;
+}
+
 template <typename T>
 __global__ void conv_tail_update_kernel(T* __restrict__ tail, const T* __restrict__ in, int64_t in_stride,
                                         const int* __restrict__ seq_start, const int* __restrict__ seq_ctx,
@@ -345,9 +384,17 @@ extern "C" int b2l_causal_conv_silu(void* out, const void* in, int64_t in_row_st
   const dim3 block(128), grid((unsigned)cdiv64(channels, 128), (unsigned)tokens);
   const dim3 grid2((unsigned)cdiv64(channels, 128), (unsigned)num_seqs);
   B2L_DISPATCH_FLOAT(dtype, "causal_conv_silu", {
-    b2l_launch(causal_conv_silu_kernel<T>, grid, block, (size_t)0, st, (T*)out, (const T*)in, in_row_stride,
-               (const T*)weight, (const T*)bias, (const T*)tail, (const int*)seq_start, (const int*)seq_ctx,
-               (const int*)seq_slot, (int)num_seqs, channels, taps);
+    constexpr int VEC = 16 / (int)sizeof(T);
+    const bool vec = channels % VEC == 0 && in_row_stride % VEC == 0 && (uintptr_t)in % 16 == 0 &&
+                     (uintptr_t)out % 16 == 0 && (uintptr_t)bias % 16 == 0 && (uintptr_t)tail % 16 == 0;
+    if (vec)
+      b2l_launch(causal_conv_silu_vec_kernel<T>, dim3((unsigned)cdiv64(channels / VEC, 128), (unsigned)tokens), block,
+                 (size_t)0, st, (T*)out, (const T*)in, in_row_stride, (const T*)weight, (const T*)bias, (const T*)tail,
+                 (const int*)seq_start, (const int*)seq_ctx, (const int*)seq_slot, (int)num_seqs, channels, taps);
+    else
+      b2l_launch(causal_conv_silu_kernel<T>, grid, block, (size_t)0, st, (T*)out, (const T*)in, in_row_stride,
+                 (const T*)weight, (const T*)bias, (const T*)tail, (const int*)seq_start, (const int*)seq_ctx,
+                 (const int*)seq_slot, (int)num_seqs, channels, taps);
     b2l_count_launch();
     if (taps > 1)
       b2l_launch(conv_tail_update_kernel<T>, grid2, block, (size_t)0, st, (T*)tail, (const T*)in, in_row_stride,

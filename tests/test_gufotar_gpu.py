@@ -65,11 +65,11 @@ def test_residual_stream_ops(dtype, tol):
     _close(relu_squared(y.to(DEV)), torch.relu(y.double()) ** 2, tol)
 
 
-@pytest.mark.parametrize("taps", [1, 2, 4, 5])
-def test_causal_conv_with_tail_over_portions(taps):
+@pytest.mark.parametrize("taps,c,extra", [(1, 37, 5), (2, 37, 5), (4, 37, 5), (5, 37, 5), (4, 40, 8), (3, 8, 0)])
+def test_causal_conv_with_tail_over_portions(taps, c, extra):
+    """Odd channel counts take the scalar kernel, multiples of 4 with an aligned column window the 16-byte one."""
     from lite_llama_b200.kernels import causal_conv_silu
 
-    c, extra = 37, 5
     w, b = torch.randn(c, taps) * 0.5, torch.randn(c) * 0.1
     seqs = {0: torch.randn(11, c), 2: torch.randn(6, c), 1: torch.randn(1, c)}        # slot -> inputs
     ref = {s: O.silu(O.causal_conv(u.double(), w.double(), b.double())[0]) for s, u in seqs.items()}
