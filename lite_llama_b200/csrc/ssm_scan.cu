@@ -53,7 +53,7 @@ __global__ void causal_conv_silu_kernel(T* __restrict__ out, const T* __restrict
 
 // The same with 16-byte accesses: one thread = VEC consecutive channels (channels, the input row stride and the
 // column window's start all multiples of VEC elements).
-template <typename T>
+template <typename T, int TAPS>     // TAPS > 0: tap count known at compile time, weights held in registers
 __global__ void causal_conv_silu_vec_kernel(T* __restrict__ out, const T* __restrict__ in, int64_t in_stride,
                                             const T* __restrict__ w, const T* __restrict__ bias,
                                             const T* __restrict__ tail, const int* __restrict__ seq_start,
@@ -74,14 +74,36 @@ __global__ void causal_conv_silu_vec_kernel(T* __restrict__ out, const T* __rest
 #pragma unroll
     for (int k = 0; k < VEC; ++k) acc[k] = to_f32(e[k]);
   }
-  for (int j = 0; j < taps; ++j) {
-    const int i = local - j;
-    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-    if (i >= 0) raw = ldg_128(in + (int64_t)(tok - j) * in_stride + c);
-    else if (ctx + i >= 0) raw = ldg_128(tail + (slot * (taps - 1) + (taps - 1 + i)) * channels + c);
-    const T* e = reinterpret_cast<const T*>(&raw);
+  if (TAPS > 0) {
+    // the VEC channels' taps are VEC * TAPS consecutive elements = TAPS 16-byte vectors
+    float wf[VEC * (TAPS > 0 ? TAPS : 1)];
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) acc[k] = fmaf(to_f32(w[(int64_t)(c + k) * taps + (taps - 1 - j)]), to_f32(e[k]), acc[k]);
+    for (int v = 0; v < TAPS; ++v) {
+      const uint4 raw = ldg_128(w + (int64_t)c * TAPS + v * VEC);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) wf[v * VEC + k] = to_f32(e[k]);
+    }
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) {
+      const int i = local - j;
+      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+      if (i >= 0) raw = ldg_128(in + (int64_t)(tok - j) * in_stride + c);
+      else if (ctx + i >= 0) raw = ldg_128(tail + (slot * (TAPS - 1) + (TAPS - 1 + i)) * channels + c);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) acc[k] = fmaf(wf[k * TAPS + (TAPS - 1 - j)], to_f32(e[k]), acc[k]);
+    }
+  } else {
+    for (int j = 0; j < taps; ++j) {
+      const int i = local - j;
+      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+      if (i >= 0) raw = ldg_128(in + (int64_t)(tok - j) * in_stride + c);
+      else if (ctx + i >= 0) raw = ldg_128(tail + (slot * (taps - 1) + (taps - 1 + i)) * channels + c);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) acc[k] = fmaf(to_f32(w[(int64_t)(c + k) * taps + (taps - 1 - j)]), to_f32(e[k]), acc[k]);
+    }
   }
   uint4 res;
   T* e = reinterpret_cast<T*>(&res);
@@ -383,14 +405,19 @@ extern "C" int b2l_causal_conv_silu(void* out, const void* in, int64_t in_row_st
   cudaStream_t st = (cudaStream_t)stream;
   const dim3 block(128), grid((unsigned)cdiv64(channels, 128), (unsigned)tokens);
   const dim3 grid2((unsigned)cdiv64(channels, 128), (unsigned)num_seqs);
+#define B2L_CONV(TP)                                                                                                 \
+  b2l_launch(causal_conv_silu_vec_kernel<T, TP>, dim3((unsigned)cdiv64(channels / VEC, 128), (unsigned)tokens), block, \
+             (size_t)0, st, (T*)out, (const T*)in, in_row_stride, (const T*)weight, (const T*)bias, (const T*)tail,  \
+             (const int*)seq_start, (const int*)seq_ctx, (const int*)seq_slot, (int)num_seqs, channels, taps)
   B2L_DISPATCH_FLOAT(dtype, "causal_conv_silu", {
     constexpr int VEC = 16 / (int)sizeof(T);
     const bool vec = channels % VEC == 0 && in_row_stride % VEC == 0 && (uintptr_t)in % 16 == 0 &&
                      (uintptr_t)out % 16 == 0 && (uintptr_t)bias % 16 == 0 && (uintptr_t)tail % 16 == 0;
-    if (vec)
-      b2l_launch(causal_conv_silu_vec_kernel<T>, dim3((unsigned)cdiv64(channels / VEC, 128), (unsigned)tokens), block,
-                 (size_t)0, st, (T*)out, (const T*)in, in_row_stride, (const T*)weight, (const T*)bias, (const T*)tail,
-                 (const int*)seq_start, (const int*)seq_ctx, (const int*)seq_slot, (int)num_seqs, channels, taps);
+    const bool wvec = (uintptr_t)weight % 16 == 0;
+    if (vec && wvec && taps == 4) B2L_CONV(4);
+    else if (vec && wvec && taps == 3) B2L_CONV(3);
+    else if (vec && wvec && taps == 2) B2L_CONV(2);
+    else if (vec) B2L_CONV(0);
     else
       b2l_launch(causal_conv_silu_kernel<T>, grid, block, (size_t)0, st, (T*)out, (const T*)in, in_row_stride,
                  (const T*)weight, (const T*)bias, (const T*)tail, (const int*)seq_start, (const int*)seq_ctx,
@@ -400,6 +427,7 @@ extern "C" int b2l_causal_conv_silu(void* out, const void* in, int64_t in_row_st
       b2l_launch(conv_tail_update_kernel<T>, grid2, block, (size_t)0, st, (T*)tail, (const T*)in, in_row_stride,
                  (const int*)seq_start, (const int*)seq_ctx, (const int*)seq_slot, channels, taps);
   });
+#undef B2L_CONV
   B2L_LAUNCH_CHECK();
   return B2L_OK;
 }
