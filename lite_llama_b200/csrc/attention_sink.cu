@@ -663,6 +663,96 @@ __global__ void attn_prepare_kernel(T* __restrict__ qkv, int64_t stride, T* __re
   }
 }
 
+// 16-byte version of attn_prepare: thread v owns vectors v, v + 256, ... of each part; q (at most kPrepQ vectors per
+// thread) stays in registers between the statistic and the scaling.
+constexpr int kPrepQ = 2;
+
+template <typename T>
+__global__ void __launch_bounds__(256) attn_prepare_vec_kernel(
+    T* __restrict__ qkv, int64_t stride, T* __restrict__ kv, int64_t kv_stride, const int* __restrict__ rows,
+    const int* __restrict__ pos, const T* __restrict__ qw, const T* __restrict__ kw, const T* __restrict__ v_first_in,
+    T* __restrict__ v_first_out, const T* __restrict__ lambda, int qn, int kn, int vn, float eps, float gain_coef,
+    double gain_every) {
+  pdl_prologue();
+  constexpr int VEC = 16 / (int)sizeof(T);
+  __shared__ float red[32];
+  const int64_t t = blockIdx.x;
+  T* q = qkv + t * stride;
+  T* k = q + qn;
+  T* v = k + kn;
+  T* dst = kv + (int64_t)rows[t] * kv_stride;
+  float gain = 1.f;
+  if (gain_every > 0.0) gain = 1.0f + gain_coef * logf((float)floor(((double)pos[t] + 1.0) / gain_every) + 1.0f);
+  {
+    uint4 raw[kPrepQ];
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < kPrepQ; ++u) {
+      const int i = (threadIdx.x + u * 256) * VEC;
+      raw[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (i < qn) raw[u] = *reinterpret_cast<const uint4*>(q + i);
+      const T* e = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+      for (int c = 0; c < VEC; ++c) { const float x = to_f32(e[c]); ss = fmaf(x, x, ss); }
+    }
+    float rr = 1.f;
+    if (qw) rr = 1.0f / sqrtf(block_sum2(ss, red) / (float)qn + eps);
+    if (qw || gain != 1.f) {
+#pragma unroll
+      for (int u = 0; u < kPrepQ; ++u) {
+        const int i = (threadIdx.x + u * 256) * VEC;
+        if (i >= qn) continue;
+        const T* e = reinterpret_cast<const T*>(&raw[u]);
+        uint4 wr = make_uint4(0u, 0u, 0u, 0u);
+        if (qw) wr = ldg_128(qw + i);
+        const T* we = reinterpret_cast<const T*>(&wr);
+        uint4 res;
+        T* re = reinterpret_cast<T*>(&res);
+#pragma unroll
+        for (int c = 0; c < VEC; ++c) re[c] = from_f32<T>(to_f32(e[c]) * rr * (qw ? to_f32(we[c]) : 1.f) * gain);
+        *reinterpret_cast<uint4*>(q + i) = res;
+      }
+    }
+  }
+  {
+    const int i = threadIdx.x * VEC;                 // kn <= 256 vectors (checked on the host)
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (i < kn) raw = *reinterpret_cast<const uint4*>(k + i);
+    const T* e = reinterpret_cast<const T*>(&raw);
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) { const float x = to_f32(e[c]); ss = fmaf(x, x, ss); }
+    float rr = 1.f;
+    if (kw) rr = 1.0f / sqrtf(block_sum2(ss, red) / (float)kn + eps);
+    if (i < kn) {
+      uint4 res = raw;
+      if (kw) {
+        const uint4 wr = ldg_128(kw + i);
+        const T* we = reinterpret_cast<const T*>(&wr);
+        T* re = reinterpret_cast<T*>(&res);
+#pragma unroll
+        for (int c = 0; c < VEC; ++c) re[c] = from_f32<T>(to_f32(e[c]) * rr * to_f32(we[c]));
+      }
+      *reinterpret_cast<uint4*>(dst + i) = res;
+    }
+  }
+  const float lam = (v_first_in && lambda) ? to_f32(lambda[0]) : 0.f;
+  for (int i = threadIdx.x * VEC; i < vn; i += 256 * VEC) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(v + i);
+    if (v_first_out) *reinterpret_cast<uint4*>(v_first_out + t * vn + i) = raw;
+    uint4 res = raw;
+    if (v_first_in) {
+      const uint4 fr = ldg_128(v_first_in + t * vn + i);
+      const T* e = reinterpret_cast<const T*>(&raw);
+      const T* fe = reinterpret_cast<const T*>(&fr);
+      T* re = reinterpret_cast<T*>(&res);
+#pragma unroll
+      for (int c = 0; c < VEC; ++c) re[c] = from_f32<T>((1.0f - lam) * to_f32(e[c]) + lam * to_f32(fe[c]));
+    }
+    *reinterpret_cast<uint4*>(dst + kn + i) = res;
+  }
+}
+
 template <typename T, bool SPLIT>
 int launch_attention(const AttnArgs& a, dim3 grid, cudaStream_t st) {
   const size_t smem = (size_t)(kRows * a.D + kKeys * (a.D + 1) + kKeys * a.Dv) * sizeof(float);
@@ -696,6 +786,17 @@ extern "C" int b2l_attn_prepare(void* qkv, int64_t qkv_row_stride, void* kv_pool
   if (tokens <= 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
   B2L_DISPATCH_FLOAT(dtype, "attn_prepare", {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    auto al = [](const void* p) { return p == nullptr || (uintptr_t)p % 16 == 0; };
+    const bool vec = q_cols % VEC == 0 && k_cols % VEC == 0 && v_cols % VEC == 0 && qkv_row_stride % VEC == 0 &&
+                     kv_row_stride % VEC == 0 && q_cols <= kPrepQ * 256 * VEC && k_cols <= 256 * VEC && al(qkv) &&
+                     al(kv_pool) && al(q_norm_weight) && al(k_norm_weight) && al(v_first_in) && al(v_first_out);
+    if (vec)
+      b2l_launch(attn_prepare_vec_kernel<T>, dim3((unsigned)tokens), dim3(256), (size_t)0, st, (T*)qkv, qkv_row_stride,
+                 (T*)kv_pool, kv_row_stride, (const int*)kv_rows_i32, (const int*)pos_i32, (const T*)q_norm_weight,
+                 (const T*)k_norm_weight, (const T*)v_first_in, (T*)v_first_out, (const T*)v_lambda, q_cols, k_cols,
+                 v_cols, eps, gain_coef, (double)gain_every);
+    else
     b2l_launch(attn_prepare_kernel<T>, dim3((unsigned)tokens), dim3(256), (size_t)0, st, (T*)qkv, qkv_row_stride,
                (T*)kv_pool, kv_row_stride, (const int*)kv_rows_i32, (const int*)pos_i32, (const T*)q_norm_weight,
                (const T*)k_norm_weight, (const T*)v_first_in, (T*)v_first_out, (const T*)v_lambda, q_cols, k_cols,

@@ -393,6 +393,60 @@ __global__ void gated_group_norm_kernel(T* __restrict__ o, const float* __restri
   }
 }
 
+// 16-byte version: one thread = VPV vectors of VEC consecutive columns, kept in registers between the two passes.
+template <typename T, int VPV>
+__global__ void gated_group_norm_vec_kernel(T* __restrict__ o, const float* __restrict__ y, const T* __restrict__ z,
+                                            int64_t z_stride, const T* __restrict__ w, int inner, int groups,
+                                            float eps) {
+  pdl_prologue();
+  constexpr int VEC = 16 / (int)sizeof(T);
+  __shared__ float red[32];
+  const int64_t t = blockIdx.y;
+  const int gs = inner / groups, base = blockIdx.x * gs, nvec = gs / VEC;
+  float keep[VPV][VEC];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPV; ++k) {
+    const int v = threadIdx.x + k * blockDim.x;
+    if (v < nvec) {
+      const int i = base + v * VEC;
+      const uint4 zr = ldg_128(z + t * z_stride + i);
+      const T* ze = reinterpret_cast<const T*>(&zr);
+#pragma unroll
+      for (int q = 0; q < VEC / 4; ++q) {
+        const float4 yv = *reinterpret_cast<const float4*>(y + t * inner + i + 4 * q);
+        keep[k][4 * q + 0] = yv.x * silu_f(to_f32(ze[4 * q + 0]));
+        keep[k][4 * q + 1] = yv.y * silu_f(to_f32(ze[4 * q + 1]));
+        keep[k][4 * q + 2] = yv.z * silu_f(to_f32(ze[4 * q + 2]));
+        keep[k][4 * q + 3] = yv.w * silu_f(to_f32(ze[4 * q + 3]));
+      }
+#pragma unroll
+      for (int c = 0; c < VEC; ++c) ss = fmaf(keep[k][c], keep[k][c], ss);
+    }
+  }
+  ss = warp_reduce_sum(ss);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  float tot = lane < nw ? red[lane] : 0.f;
+  tot = warp_reduce_sum(tot);
+  const float rr = 1.0f / sqrtf(tot / (float)gs + eps);
+#pragma unroll
+  for (int k = 0; k < VPV; ++k) {
+    const int v = threadIdx.x + k * blockDim.x;
+    if (v < nvec) {
+      const int i = base + v * VEC;
+      const uint4 wr = ldg_128(w + i);
+      const T* we = reinterpret_cast<const T*>(&wr);
+      uint4 res;
+      T* re = reinterpret_cast<T*>(&res);
+#pragma unroll
+      for (int c = 0; c < VEC; ++c) re[c] = from_f32<T>(keep[k][c] * rr * to_f32(we[c]));
+      *reinterpret_cast<uint4*>(o + t * inner + i) = res;
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" int b2l_causal_conv_silu(void* out, const void* in, int64_t in_row_stride, const void* weight,
@@ -491,6 +545,35 @@ extern "C" int b2l_gated_group_norm(void* out, const void* y_f32, const void* z,
   const int gs = inner / groups;
   const int threads = gs >= 1024 ? 256 : (gs >= 256 ? 128 : (gs >= 64 ? 64 : 32));
   const int vpt = (gs + threads - 1) / threads;
+  {
+    int rc = 1;
+    B2L_DISPATCH_FLOAT(dtype, "gated_group_norm", {
+      constexpr int VEC = 16 / (int)sizeof(T);
+      const bool vec = gs % VEC == 0 && z_row_stride % VEC == 0 && (uintptr_t)z % 16 == 0 && (uintptr_t)y_f32 % 16 == 0 &&
+                       (uintptr_t)out % 16 == 0 && (uintptr_t)weight % 16 == 0;
+      const int nvec = gs / VEC;
+      int vth = ((nvec + 31) / 32) * 32;
+      if (vth > 256) vth = 256;
+      const int vpv = vec ? (nvec + vth - 1) / vth : 99;
+      if (vpv <= 4) {
+        const dim3 g2((unsigned)groups, (unsigned)rows), b2((unsigned)vth);
+        if (vpv <= 1)
+          b2l_launch(gated_group_norm_vec_kernel<T, 1>, g2, b2, (size_t)0, st, (T*)out, (const float*)y_f32, (const T*)z,
+                     z_row_stride, (const T*)weight, inner, groups, eps);
+        else if (vpv <= 2)
+          b2l_launch(gated_group_norm_vec_kernel<T, 2>, g2, b2, (size_t)0, st, (T*)out, (const float*)y_f32, (const T*)z,
+                     z_row_stride, (const T*)weight, inner, groups, eps);
+        else
+          b2l_launch(gated_group_norm_vec_kernel<T, 4>, g2, b2, (size_t)0, st, (T*)out, (const float*)y_f32, (const T*)z,
+                     z_row_stride, (const T*)weight, inner, groups, eps);
+        rc = 0;
+      }
+    });
+    if (rc == 0) {
+      B2L_LAUNCH_CHECK();
+      return B2L_OK;
+    }
+  }
 #define B2L_GGN(V)                                                                                                  \
   b2l_launch(gated_group_norm_kernel<T, V>, dim3((unsigned)groups, (unsigned)rows), dim3(threads), (size_t)0, st,  \
              (T*)out, (const float*)y_f32, (const T*)z, z_row_stride, (const T*)weight, inner, groups, eps)
