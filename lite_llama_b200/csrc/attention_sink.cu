@@ -35,7 +35,8 @@ struct AttnArgs {
   float scale, softcap;
 };
 
-template <typename T, int DVJ, bool SPLIT>
+// ---- tiled mode on the CUDA cores (fp32 activations, or head sizes the tensor-core tiles do not take) ------------
+template <typename T, int DVJ>
 __global__ void __launch_bounds__(kWarps * 32) sink_attention_kernel(AttnArgs a) {
   pdl_prologue();
   extern __shared__ float smem[];
@@ -49,11 +50,10 @@ __global__ void __launch_bounds__(kWarps * 32) sink_attention_kernel(AttnArgs a)
   const int hchunks = (per + a.PH - 1) / a.PH;
   const int g = blockIdx.y / hchunks, h_first = g * per + (blockIdx.y % hchunks) * a.PH;
   const int h_count = min(a.PH, g * per + per - h_first);
-  const int t0 = SPLIT ? 0 : blockIdx.x * a.BQ;
+  const int t0 = blockIdx.x * a.BQ;
   if (t0 >= qlen) return;
-  const int t_count = SPLIT ? 1 : min(a.BQ, qlen - t0);
-  const int key_lo = SPLIT ? blockIdx.x * a.chunk : 0;
-  const int key_hi = SPLIT ? min(key_lo + a.chunk, ctx + 1) : ctx + t0 + t_count;    // exclusive
+  const int t_count = min(a.BQ, qlen - t0);
+  const int key_lo = 0, key_hi = ctx + t0 + t_count;    // exclusive
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const T* q = (const T*)a.q;
   const T* kv = (const T*)a.kv;
@@ -127,15 +127,7 @@ __global__ void __launch_bounds__(kWarps * 32) sink_attention_kernel(AttnArgs a)
   for (int i = 0; i < kRowsPerWarp; ++i) {
     if (row_pos[i] < 0) continue;
     const int r = warp * kRowsPerWarp + i, tl = r / a.PH, hl = r - tl * a.PH, h = h_first + hl;
-    if (SPLIT) {
-      float* dst = a.part + (((int64_t)z * a.H + h) * a.nsplit + blockIdx.x) * (Dv + 2);
-      if (lane == 0) { dst[0] = m[i]; dst[1] = l[i]; }
-#pragma unroll
-      for (int j = 0; j < DVJ; ++j) {
-        const int d = lane + 32 * j;
-        if (d < Dv) dst[2 + d] = acc[i][j];
-      }
-    } else {
+    {
       float mf = m[i], den = l[i], num = 1.f;
       if (a.sink) {
         const float sk = to_f32(((const T*)a.sink)[h]);
@@ -753,7 +745,7 @@ __global__ void __launch_bounds__(256) attn_prepare_vec_kernel(
   }
 }
 
-template <typename T, bool SPLIT>
+template <typename T>
 int launch_attention(const AttnArgs& a, dim3 grid, cudaStream_t st) {
   const size_t smem = (size_t)(kRows * a.D + kKeys * (a.D + 1) + kKeys * a.Dv) * sizeof(float);
   B2L_REQUIRE((int64_t)smem <= b2l_max_smem_optin(), "sink_attention: head sizes %d / %d need %lld bytes of shared memory",
@@ -763,8 +755,8 @@ int launch_attention(const AttnArgs& a, dim3 grid, cudaStream_t st) {
 #define B2L_ATTN(J)                                                                                           \
   do {                                                                                                        \
     static int cache[64] = {0};                                                                               \
-    B2L_CUDA_CHECK(b2l_ensure_dynamic_smem(sink_attention_kernel<T, J, SPLIT>, (int)smem, cache));            \
-    b2l_launch(sink_attention_kernel<T, J, SPLIT>, grid, dim3(kWarps * 32), smem, st, a);                     \
+    B2L_CUDA_CHECK(b2l_ensure_dynamic_smem(sink_attention_kernel<T, J>, (int)smem, cache));                   \
+    b2l_launch(sink_attention_kernel<T, J>, grid, dim3(kWarps * 32), smem, st, a);                            \
   } while (0)
   if (dvj <= 2) B2L_ATTN(2);
   else if (dvj <= 4) B2L_ATTN(4);
@@ -843,9 +835,6 @@ extern "C" int b2l_sink_attention(void* out, int64_t out_row_stride, const void*
     const int64_t need = b2l_sink_attention_workspace_bytes(num_seqs, heads, v_head_dim, num_splits);
     B2L_REQUIRE(workspace && workspace_bytes >= need, "sink_attention: workspace too small (%lld < %lld)",
                 (long long)workspace_bytes, (long long)need);
-    a.BQ = 1;
-    a.PH = per < kRows ? per : kRows;
-    const dim3 grid((unsigned)num_splits, (unsigned)(kv_heads * hchunks), (unsigned)num_seqs);
     int rc = B2L_OK;
     B2L_DISPATCH_FLOAT(dtype, "sink_attention", { rc = launch_attention_split<T>(a, num_seqs, st); });
     if (rc != B2L_OK) return rc;
@@ -863,6 +852,6 @@ extern "C" int b2l_sink_attention(void* out, int64_t out_row_stride, const void*
   }
   const dim3 grid((unsigned)((max_q_len + a.BQ - 1) / a.BQ), (unsigned)(kv_heads * hchunks), (unsigned)num_seqs);
   int rc = B2L_OK;
-  B2L_DISPATCH_FLOAT(dtype, "sink_attention", { rc = launch_attention<T, false>(a, grid, st); });
+  B2L_DISPATCH_FLOAT(dtype, "sink_attention", { rc = launch_attention<T>(a, grid, st); });
   return rc;
 }

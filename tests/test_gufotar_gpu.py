@@ -262,6 +262,11 @@ CONFIGS = {
                                         O.mamba2_layer(heads=5, vdim=4, state=33, groups=5, norm_groups=5, conv=5),
                                         O.attention_layer(heads=2, kv_heads=2, dim=12, vdim=36, v_mix=False)],
                                        width=36, vocab=61),
+    # sizes in steps of 8: the 16-byte kernels, the tensor-core attention tiles (bf16), two columns per lane in the scan
+    "aligned": lambda: O.make_config([O.mamba2_layer(heads=4, vdim=40, state=24, groups=2, norm_groups=2, conv=4, ff=64),
+                                      O.attention_layer(heads=4, kv_heads=2, dim=32, vdim=40, every=16),
+                                      O.attention_layer(heads=8, kv_heads=1, dim=16, vdim=80, every=16, ff=0)],
+                                     width=64, vocab=128),
     "recurrent_only": lambda: O.make_config([O.mamba2_layer(ff=32), O.mamba2_layer(groups=1, norm_groups=1, conv=4)]),
     "attention_only": lambda: O.make_config([O.attention_layer(), O.attention_layer(v_mix=False, ff=0),
                                              O.attention_layer()], width=48),
@@ -374,16 +379,18 @@ def test_long_decoding_crosses_key_split_edges():
     _close(got, ref, 1e-4)
 
 
-def test_bf16_serving_precision_stays_within_a_few_roundings():
-    cfg = CONFIGS["mixed"]()
+@pytest.mark.parametrize("name,length,cuts", [("mixed", 40, [13, 2, 9]), ("aligned", 150, [70, 3, 66])])
+def test_bf16_serving_precision_stays_within_a_few_roundings(name, length, cuts):
+    cfg = CONFIGS[name]()
     w = O.random_model(cfg, seed=11)
-    toks = _tokens(cfg, 40, 12)
+    toks = _tokens(cfg, length, 12)
     ref = O.Oracle(cfg, w).forward(toks)
-    runner = _runner(cfg, w, dtype=torch.bfloat16)
-    got = _feed(runner, runner.open_request(), toks, [13, 2, 9])
-    d = got.double().cpu() - ref
-    rel = (d - d.mean(-1, keepdim=True)).pow(2).mean(-1).sqrt() / ref.std()
-    assert rel.max().item() < 0.06, rel.max().item()
+    for plan in (cuts, [length]):
+        runner = _runner(cfg, w, dtype=torch.bfloat16)
+        got = _feed(runner, runner.open_request(), toks, plan)
+        d = got.double().cpu() - ref
+        rel = (d - d.mean(-1, keepdim=True)).pow(2).mean(-1).sqrt() / ref.std()
+        assert rel.max().item() < 0.06, rel.max().item()
 
 
 def test_checkpoint_directory_and_greedy_generation_through_the_engine(tmp_path):
