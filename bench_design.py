@@ -4,7 +4,8 @@ uniform rotary decoder: same width, layer count, attention geometry and feed-for
 new path timed alone against its like kernel with the fraction of the measured roofline each reaches.
 
 Timing: CUDA events on the launching stream, >= 3 warm-up runs, a 256 MiB write between timed runs (larger than the
-126 MB L2), median of the timed runs.  Step figures include the host work of a step (metadata build, allocation).
+126 MB L2), median of the timed runs.  Step figures include the host work of a step (metadata build, allocation);
+prefill steps are eager, decode steps replay each model's captured graph.
 """
 
 from __future__ import annotations
@@ -91,6 +92,7 @@ def step_throughput(sz, batch, prompt, dev, dtype, flush) -> dict:
     ids = torch.randint(0, sz["vocab"], (batch, prompt), generator=gen)
     # ---- the layer-list design: ragged steps through ModelRunner.forward_ragged
     r = build_gufotar(sz, batch, max_pos, dev, dtype)
+    r.enable_ragged_decode_graphs(widths=(batch,), ctx_buckets=(max_pos,))     # decode steps replay a captured graph
     reqs = []
 
     def g_prefill():
@@ -115,8 +117,9 @@ def step_throughput(sz, batch, prompt, dev, dtype, flush) -> dict:
                       "decode_tok_s": batch / dec * 1e3, "weight_bytes_per_step": r.model.w.nbytes_per_step()}
     del r, reqs
     torch.cuda.empty_cache()
-    # ---- the closest existing model: uniform rotary decoder, padded-rectangle prefill + one-token decode (eager)
+    # ---- the closest existing model: uniform rotary decoder, padded-rectangle prefill + one-token decode
     u = build_uniform(sz, batch, max_pos, dev, dtype)
+    u.enable_cuda_graph(batch_sizes=(batch,), seq_len_buckets=(max_pos,))      # likewise
     lens = torch.full((batch,), prompt, dtype=torch.int64, device=dev)
     idx = torch.arange(batch, dtype=torch.int64, device=dev)
     pos = torch.arange(prompt, device=dev).repeat(batch, 1)

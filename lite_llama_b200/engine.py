@@ -44,7 +44,10 @@ class GenerationRequest:
 
 
 class Engine:
-    def __init__(self, runner: ModelRunner, max_step_tokens: int = 2048, max_portion: int = 512) -> None:
+    def __init__(self, runner: ModelRunner, max_step_tokens: int = 2048, max_portion: int = 512,
+                 decode_graphs: bool = True) -> None:
+        """``decode_graphs``: capture the ragged-step models' decode steps as CUDA graphs (one per batch width and
+        context bucket) when the engine starts on a runner with no live request; pure decode steps then replay."""
         self.runner = runner
         self.max_step_tokens = max(1, max_step_tokens)
         self.max_portion = max(1, max_portion)
@@ -57,6 +60,8 @@ class Engine:
         if runner.ragged_steps:
             self._slots_free = runner.max_request_num
             self._pool = runner.kv_cache_manager.max_num_tokens
+            if decode_graphs and hasattr(runner, "enable_ragged_decode_graphs"):
+                runner.enable_ragged_decode_graphs()
         else:
             self._sb = runner.enable_slot_kv_cache()
             self._free_slots = list(range(self._sb.num_slots - 1, -1, -1))

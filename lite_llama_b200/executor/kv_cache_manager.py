@@ -12,6 +12,11 @@ Allocation strategies, cheapest first (kv_cache_manager.py:270-300):
   * any ``need_size`` free rows.
 Rows are released per reference (``release_ref`` / ``free``), all at once (``free_all``), or handed to an
 external owner for good (``claim``: the slot layout of continuous batching).
+
+Ragged-step models allocate every step, so their runner drives the pool through a HOST free list instead
+(``alloc_rows_host`` / ``release_rows_host``): row numbers are Python ints that travel to the device inside the
+step's one metadata copy, and no step waits for a device scan of the reference counts.  A pool is driven through one
+of the two schemes, not both: once the host list is in use the device-scan allocators refuse to run.
 """
 
 from __future__ import annotations
@@ -42,6 +47,7 @@ class KVCacheManager:
         self.kv_mem_use_state = torch.zeros(self.max_num_tokens, dtype=torch.int32, device=device)
         self._bump_cursor = 0
         self._bump_is_exact = True
+        self._host_free: list[int] | None = None          # host free list (ragged-step runners), lowest row on top
         if row_widths is not None:
             if len(row_widths) != num_layers:
                 raise ValueError("row_widths needs one entry per cached layer")
@@ -52,8 +58,35 @@ class KVCacheManager:
                 for _ in range(num_layers)
             ]
 
+    # ------------------------------------------------------- host free list #
+    def _host_list(self) -> list[int]:
+        if self._host_free is None:
+            if self.can_use_mem_size == self.max_num_tokens:
+                self._host_free = list(range(self.max_num_tokens - 1, -1, -1))
+            else:                                          # rows are already out: read the counts once
+                self._host_free = sorted((self.kv_mem_use_state == 0).nonzero().view(-1).tolist(), reverse=True)
+        return self._host_free
+
+    def alloc_rows_host(self, need_size: int) -> list[int] | None:
+        """``need_size`` free rows as Python ints (lowest first), or ``None`` -- and then nothing changes."""
+        free = self._host_list()
+        if need_size > len(free):
+            return None
+        rows = [free.pop() for _ in range(need_size)]
+        self.can_use_mem_size -= need_size
+        self._bump_is_exact = False
+        return rows
+
+    def release_rows_host(self, rows: list[int]) -> None:
+        """Give rows handed out by :meth:`alloc_rows_host` back (each exactly once)."""
+        free = self._host_list()
+        free.extend(sorted(rows, reverse=True))
+        self.can_use_mem_size += len(rows)
+
     # ------------------------------------------------------------ allocation #
     def _free_rows(self) -> torch.Tensor:
+        if self._host_free is not None:
+            raise RuntimeError("this pool is driven through the host free list (alloc_rows_host / release_rows_host)")
         return (self.kv_mem_use_state == 0).nonzero().view(-1)
 
     @torch.no_grad()
@@ -90,6 +123,8 @@ class KVCacheManager:
 
         On the append-only path this is a view of a constant arange plus one in-place add on the
         device -- no host read, no synchronisation (a decode step calls it once)."""
+        if self._host_free is not None:
+            raise RuntimeError("this pool is driven through the host free list (alloc_rows_host / release_rows_host)")
         if self._bump_is_exact and self._bump_cursor + need_size <= self.max_num_tokens:
             start = self._bump_cursor
             self.kv_mem_use_state[start : start + need_size] += 1
@@ -138,3 +173,5 @@ class KVCacheManager:
         self.can_use_mem_size = self.max_num_tokens
         self._bump_cursor = 0
         self._bump_is_exact = True
+        if self._host_free is not None:
+            self._host_free = list(range(self.max_num_tokens - 1, -1, -1))

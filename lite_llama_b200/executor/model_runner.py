@@ -86,6 +86,53 @@ class _CapturedDecode:
         return self.logits[:n]
 
 
+class _CapturedRaggedDecode:
+    """One captured decode step of a ragged-step model: ``width`` sequences bring one token each, contexts up to
+    ``ctx_cap`` keys.  The step's metadata lives in one persistent device buffer that ``replay`` refills with a single
+    host-to-device copy (pool rows included); the attention key split is sized for ``ctx_cap`` at capture and
+    serves every shorter context (ranges past a sequence's end are empty).  Same kernels, same order as the eager
+    step, so the logits are the eager step's."""
+
+    def __init__(self, runner: "ModelRunner", width: int, ctx_cap: int) -> None:
+        dev = runner.device
+        self.runner, self.width, self.ctx_cap = runner, width, ctx_cap
+        # packed int32: ids | positions | cached lengths | slots | table indices | pool rows
+        self.packed = torch.zeros(6 * width, dtype=torch.int32, device=dev)
+        self.ids, self.pos, self.ctx, self.slot, self.tidx32, self.rows = (
+            self.packed[i * width:(i + 1) * width] for i in range(6))
+        self.slot.copy_(torch.arange(width, dtype=torch.int32, device=dev))
+        self.tidx32.copy_(torch.arange(width, dtype=torch.int32, device=dev) * runner.max_seq_len)
+        self.rows.copy_(torch.arange(width, dtype=torch.int32, device=dev))
+        self.tidx = torch.zeros(width, dtype=torch.int64, device=dev)
+        ar = torch.arange(width + 1, dtype=torch.int32, device=dev)
+        self.batch = RaggedBatch(tokens=width, num_seqs=width, seq_start=ar, seq_ctx=self.ctx, seq_slot=self.slot,
+                                 positions=self.pos, kv_rows=self.rows, portion_list=ar[:0], single_list=ar[:width].clone(),
+                                 num_portions=0, num_singles=width, max_portion=0, max_single_ctx=ctx_cap - 1)
+        self.graph = torch.cuda.CUDAGraph()
+        # warm-up (lazy module loads, workspaces) on a side stream, then capture; both write only rows / slots of
+        # sequences WITHOUT cached tokens, which nothing reads -- but they do write them: no request may be live
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self._ops()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(self.graph):
+            self.logits = self._ops()
+
+    def _ops(self) -> torch.Tensor:
+        r = self.runner
+        self.tidx.copy_(self.tidx32)
+        r.b_req_tokens_table.view(-1).index_copy_(0, self.tidx, self.rows)
+        return r.model.forward(self.ids, self.batch, r.kv_buffer_of, r.b_req_tokens_table, r.state_manager, None)
+
+    def replay(self, packed_host: torch.Tensor) -> torch.Tensor:
+        self.packed.copy_(packed_host, non_blocking=True)
+        self.graph.replay()
+        return self.logits
+
+
 class GreedyDecodeLoop:
     """A whole greedy decode step captured as ONE CUDA graph: token-table update, model forward,
     argmax, and the on-device bookkeeping the reference's hot loop does per step
@@ -194,7 +241,7 @@ class RequestState:
     def __init__(self, slot: int) -> None:
         self.slot = slot
         self.num_cached = 0
-        self.rows: list[torch.Tensor] = []
+        self.rows: list[int] = []
 
 
 class ModelRunner:
@@ -208,6 +255,7 @@ class ModelRunner:
         self._graphs: dict[tuple[int, int], _CapturedDecode] = {}
         self._graph_batches: tuple[int, ...] = ()
         self._graph_buckets: tuple[int, ...] = ()
+        self._ragged_graphs: dict[tuple[int, int], _CapturedRaggedDecode] = {}
         if self.ragged_steps:
             self._init_layered(config, weights, max_gpu_num_blocks, max_requests or 4)
             return
@@ -266,13 +314,35 @@ class ModelRunner:
         weights = arch.map_weights(cfg, read_checkpoint(model_dir), device, dtype)
         return cls(cfg, weights, max_tokens, device=device, dtype=dtype, max_requests=max_requests)
 
+    def enable_ragged_decode_graphs(self, widths: tuple[int, ...] | None = None,
+                                    ctx_buckets: tuple[int, ...] = DEFAULT_SEQ_LEN_BUCKETS) -> None:
+        """Capture one decode-step graph per (number of sequences, context bucket); steps in which every request
+        brings exactly one token and all logits are wanted then replay it (the counterpart of ``enable_cuda_graph``
+        for ragged-step models).  Must run while no request is live: the capture warm-up writes pool rows and state
+        slots.  Capture OOM leaves the eager path."""
+        if not self.ragged_steps:
+            raise RuntimeError("enable_ragged_decode_graphs() is for ragged-step models")
+        if self.state_manager.free_slots != self.max_request_num or \
+                self.kv_cache_manager.can_use_mem_size != self.kv_cache_manager.max_num_tokens:
+            raise RuntimeError("enable_ragged_decode_graphs() must run before any request is admitted")
+        widths = tuple(w for w in (widths or range(1, self.max_request_num + 1))
+                       if 1 <= w <= min(self.max_request_num, self.kv_cache_manager.max_num_tokens))
+        caps = sorted({min(b, self.max_seq_len) for b in ctx_buckets} | {self.max_seq_len})
+        try:
+            for w in widths:
+                for c in caps:
+                    if (w, c) not in self._ragged_graphs:
+                        self._ragged_graphs[(w, c)] = _CapturedRaggedDecode(self, w, c)
+        except torch.cuda.OutOfMemoryError:
+            self._ragged_graphs.clear()
+
     def open_request(self) -> RequestState:
         return RequestState(self.state_manager.acquire())
 
     def close_request(self, req: RequestState) -> None:
         """Give the request's pool rows and its slot back."""
         if req.rows:
-            self.kv_cache_manager.release_ref(torch.cat(req.rows))
+            self.kv_cache_manager.release_rows_host(req.rows)
             req.rows = []
         self.state_manager.release(req.slot)
         req.num_cached = 0
@@ -285,7 +355,9 @@ class ModelRunner:
                        want: list[int] | None = None) -> torch.Tensor:
         """One step over a flat batch: ``entries[i] = (request, its next tokens)``; ``want`` = flat indices of the
         tokens whose logits are returned (default: the last token of every entry).  Allocates the step's pool
-        rows, extends the request table, runs the decoder, and advances every request's cached length."""
+        rows, extends the request table, runs the decoder, and advances every request's cached length.  A step that
+        replays a captured graph (``enable_ragged_decode_graphs``) returns the graph's output buffer, which the next
+        replay of that graph overwrites."""
         lens = [len(t) for _, t in entries]
         if not entries or min(lens) < 1:
             raise ValueError("forward_ragged: every entry brings at least one token")
@@ -297,7 +369,7 @@ class ModelRunner:
         for c, n in zip(ctxs, lens):
             if c + n > self.max_seq_len:
                 raise ValueError(f"sequence of {c + n} tokens exceeds max_seq_len {self.max_seq_len}")
-        rows = self.kv_cache_manager.alloc_kvcache(total)
+        rows = self.kv_cache_manager.alloc_rows_host(total)
         if rows is None:
             raise RuntimeError(f"KV pool exhausted: {total} rows wanted, {self.kv_cache_manager.can_use_mem_size} free")
         flat_ids: list[int] = []
@@ -306,7 +378,7 @@ class ModelRunner:
         for (req, toks), n, c in zip(entries, lens, ctxs):
             flat_ids.extend(toks)
             table_idx.extend(range(req.slot * self.max_seq_len + c, req.slot * self.max_seq_len + c + n))
-            req.rows.append(rows[at:at + n])
+            req.rows.extend(rows[at:at + n])
             at += n
         if min(flat_ids) < 0 or max(flat_ids) >= self.vocab_size:
             raise ValueError("token id outside the vocabulary")
@@ -315,10 +387,17 @@ class ModelRunner:
             for n in lens:
                 at += n
                 want.append(at - 1)
-        host = torch.tensor(flat_ids + table_idx + list(want), dtype=torch.int32)
+        if self._ragged_graphs and max(lens) == 1 and list(want) == list(range(total)):
+            cap = min((c for (w, c) in self._ragged_graphs if w == total and c >= max(ctxs) + 1), default=None)
+            if cap is not None:
+                host = torch.tensor(flat_ids + ctxs + ctxs + slots + table_idx + rows, dtype=torch.int32)   # positions = ctxs
+                logits = self._ragged_graphs[(total, cap)].replay(host.pin_memory())
+                for req, _ in entries:
+                    req.num_cached += 1
+                return logits
+        host = torch.tensor(flat_ids + table_idx + rows + list(want), dtype=torch.int32)
         dev = (host.pin_memory() if torch.cuda.is_available() else host).to(self.device, non_blocking=True)
-        ids, tidx, want_rows = dev[:total], dev[total:2 * total], dev[2 * total:]
-        rows32 = rows.to(torch.int32)
+        ids, tidx, rows32, want_rows = dev[:total], dev[total:2 * total], dev[2 * total:3 * total], dev[3 * total:]
         self.b_req_tokens_table.view(-1).index_copy_(0, tidx.long(), rows32)
         batch = RaggedBatch.build(lens, ctxs, slots, rows32, self.device)
         logits = self.model.forward(ids, batch, self.kv_buffer_of, self.b_req_tokens_table, self.state_manager,

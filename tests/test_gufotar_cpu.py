@@ -111,6 +111,23 @@ def test_ragged_batch_metadata():
     assert (b.max_portion, b.max_single_ctx, b.num_portions, b.num_singles) == (5, 9, 2, 2)
 
 
+def test_host_free_list_of_the_pool():
+    from lite_llama_b200.executor.kv_cache_manager import KVCacheManager
+
+    m = KVCacheManager(2, 0, 0, 10, dtype=torch.float32, device="cpu", row_widths=[6, 4])
+    assert [tuple(b.shape) for b in m.gpu_kv_buffer] == [(10, 6), (10, 4)]
+    a = m.alloc_rows_host(4)
+    b = m.alloc_rows_host(5)
+    assert a == [0, 1, 2, 3] and b == [4, 5, 6, 7, 8] and m.can_use_mem_size == 1
+    assert m.alloc_rows_host(2) is None and m.can_use_mem_size == 1
+    m.release_rows_host(a)
+    assert m.alloc_rows_host(3) == [0, 1, 2] and m.can_use_mem_size == 2        # freed rows are handed out again
+    with pytest.raises(RuntimeError):
+        m.alloc_kvcache(1)                                                       # one scheme per pool
+    m.free_all()
+    assert m.can_use_mem_size == 10 and m.alloc_rows_host(10) == list(range(10))
+
+
 def test_state_slots_change_hands():
     from lite_llama_b200.executor.layered_decoder import parse_gufotar_config
     from lite_llama_b200.executor.state_manager import RecurrentStateManager

@@ -393,6 +393,33 @@ def test_bf16_serving_precision_stays_within_a_few_roundings(name, length, cuts)
         assert rel.max().item() < 0.06, rel.max().item()
 
 
+def test_captured_decode_steps_equal_eager_ones():
+    """Pure decode steps replayed from the captured graphs (two context buckets, widths 1-3, requests joining and
+    leaving) give the eager step's logits up to rounding; steps with a prompt portion stay eager."""
+    cfg = CONFIGS["mixed"]()
+    w = O.random_model(cfg, seed=21)
+    prompts = [_tokens(cfg, n, 30 + n) for n in (70, 5, 33)]
+    tails = [_tokens(cfg, 12, 40 + i) for i in range(3)]
+    outs = []
+    for graphs in (False, True):
+        runner = _runner(cfg, w, max_tokens=256, max_requests=3)
+        if graphs:
+            runner.enable_ragged_decode_graphs(ctx_buckets=(64, 256))
+            assert sorted(runner._ragged_graphs) == [(b, c) for b in (1, 2, 3) for c in (64, 256)]
+        reqs = [runner.open_request() for _ in prompts]
+        got = [runner.forward_ragged([(r, p) for r, p in zip(reqs, prompts)])]
+        for step in range(12):
+            live = [i for i in range(3) if not (i == 1 and step >= 6)]          # request 1 leaves half way
+            if step == 6:
+                runner.close_request(reqs[1])
+            got.append(runner.forward_ragged([(reqs[i], [tails[i][step]]) for i in live]).clone())   # replays reuse one buffer
+        outs.append(torch.cat(got).float().cpu())
+    _close(outs[1], outs[0], 1e-5)            # the key split is sized for the bucket: another summation order
+    orc = O.Oracle(cfg, w)
+    ref = orc.forward(prompts[0] + tails[0], seq=0)
+    _close(outs[1][[0] + [3 + 3 * k for k in range(6)]], ref[[69] + [70 + k for k in range(6)]], 1e-4)
+
+
 def test_checkpoint_directory_and_greedy_generation_through_the_engine(tmp_path):
     import json
 
