@@ -325,8 +325,9 @@ class ModelRunner:
         if self.state_manager.free_slots != self.max_request_num or \
                 self.kv_cache_manager.can_use_mem_size != self.kv_cache_manager.max_num_tokens:
             raise RuntimeError("enable_ragged_decode_graphs() must run before any request is admitted")
-        widths = tuple(w for w in (widths or range(1, self.max_request_num + 1))
-                       if 1 <= w <= min(self.max_request_num, self.kv_cache_manager.max_num_tokens))
+        if widths is None:       # every width of a small engine; the captured batch sizes of a large one (others run eager)
+            widths = tuple(range(1, self.max_request_num + 1)) if self.max_request_num <= 8 else DEFAULT_BATCH_SIZES
+        widths = tuple(w for w in widths if 1 <= w <= min(self.max_request_num, self.kv_cache_manager.max_num_tokens))
         caps = sorted({min(b, self.max_seq_len) for b in ctx_buckets} | {self.max_seq_len})
         try:
             for w in widths:
