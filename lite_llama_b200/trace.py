@@ -46,6 +46,8 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, max_reques
             req = live.get(e["id"])
             if req is None:
                 req = live[e["id"]] = runner.open_request()
+            if not e["tokens"]:                      # admitted, nothing to run yet
+                continue
             entries.append((req, list(e["tokens"])))
             want.extend(at + int(i) for i in e.get("want", []))
             at += len(e["tokens"])
