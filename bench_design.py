@@ -10,6 +10,7 @@ prefill steps are eager, decode steps replay each model's captured graph.
 
 from __future__ import annotations
 
+import gc
 import json
 import math
 import statistics
@@ -116,6 +117,7 @@ def step_throughput(sz, batch, prompt, dev, dtype, flush) -> dict:
     out["gufotar"] = {"prefill_ms": pre, "prefill_tok_s": batch * prompt / pre * 1e3, "decode_ms": dec,
                       "decode_tok_s": batch / dec * 1e3, "weight_bytes_per_step": r.model.w.nbytes_per_step()}
     del r, reqs
+    gc.collect()
     torch.cuda.empty_cache()
     # ---- the closest existing model: uniform rotary decoder, padded-rectangle prefill + one-token decode
     u = build_uniform(sz, batch, max_pos, dev, dtype)
@@ -146,6 +148,7 @@ def step_throughput(sz, batch, prompt, dev, dtype, flush) -> dict:
     out["uniform_decoder"] = {"prefill_ms": pre, "prefill_tok_s": batch * prompt / pre * 1e3, "decode_ms": dec,
                               "decode_tok_s": batch / dec * 1e3, "weight_bytes_per_step": u.model.w.nbytes_per_step()}
     del u
+    gc.collect()
     torch.cuda.empty_cache()
     return out
 

@@ -218,17 +218,32 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(AttnArgs a) {
   auto issue = [&](int k0, int st) {
     uint8_t* kdst = smem_raw + st * kStage;
     uint8_t* vdst = kdst + kTileN * KP;
-    for (int i = tid; i < kTileN * (DP / 8); i += 128) {
-      const int r = i / (DP / 8), c = (i - r * (DP / 8)) * 8;
-      if (k0 + r < key_hi && c < D)
-        cp_async_16(smem_u32(kdst + r * KP + c * 2), kv + (int64_t)trow[k0 + r] * a.kv_stride + g * D + c);
+    // the pool rows of this thread's copies first (independent loads), then the copies
+    constexpr int JK = kTileN * (DP / 8) / 128, JV = kTileN * (DVP / 8) / 128;
+    int rk[JK], rv[JV];
+#pragma unroll
+    for (int j = 0; j < JK; ++j) {
+      const int r = (tid + 128 * j) / (DP / 8);
+      rk[j] = k0 + r < key_hi ? trow[k0 + r] : -1;
+    }
+#pragma unroll
+    for (int j = 0; j < JV; ++j) {
+      const int r = (tid + 128 * j) / (DVP / 8);
+      rv[j] = k0 + r < key_hi ? trow[k0 + r] : -1;
+    }
+#pragma unroll
+    for (int j = 0; j < JK; ++j) {
+      const int i = tid + 128 * j, r = i / (DP / 8), c = (i - r * (DP / 8)) * 8;
+      if (rk[j] >= 0 && c < D)
+        cp_async_16(smem_u32(kdst + r * KP + c * 2), kv + (int64_t)rk[j] * a.kv_stride + g * D + c);
       else
         *reinterpret_cast<uint4*>(kdst + r * KP + c * 2) = make_uint4(0u, 0u, 0u, 0u);
     }
-    for (int i = tid; i < kTileN * (DVP / 8); i += 128) {
-      const int r = i / (DVP / 8), c = (i - r * (DVP / 8)) * 8;
-      if (k0 + r < key_hi && c < Dv)
-        cp_async_16(smem_u32(vdst + r * VP + c * 2), kv + (int64_t)trow[k0 + r] * a.kv_stride + a.G * D + g * Dv + c);
+#pragma unroll
+    for (int j = 0; j < JV; ++j) {
+      const int i = tid + 128 * j, r = i / (DVP / 8), c = (i - r * (DVP / 8)) * 8;
+      if (rv[j] >= 0 && c < Dv)
+        cp_async_16(smem_u32(vdst + r * VP + c * 2), kv + (int64_t)rv[j] * a.kv_stride + a.G * D + g * Dv + c);
       else
         *reinterpret_cast<uint4*>(vdst + r * VP + c * 2) = make_uint4(0u, 0u, 0u, 0u);
     }

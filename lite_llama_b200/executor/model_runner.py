@@ -95,7 +95,11 @@ class _CapturedRaggedDecode:
 
     def __init__(self, runner: "ModelRunner", width: int, ctx_cap: int) -> None:
         dev = runner.device
-        self.runner, self.width, self.ctx_cap = runner, width, ctx_cap
+        self.width, self.ctx_cap = width, ctx_cap
+        # no reference to the runner itself: a runner <-> graph cycle would leave the graphs to the garbage collector,
+        # which may then release them in the middle of somebody else's capture
+        self._model, self._table, self._kv, self._states = (runner.model, runner.b_req_tokens_table, runner.kv_buffer_of,
+                                                            runner.state_manager)
         # packed int32: ids | positions | cached lengths | slots | table indices | pool rows
         self.packed = torch.zeros(6 * width, dtype=torch.int32, device=dev)
         self.ids, self.pos, self.ctx, self.slot, self.tidx32, self.rows = (
@@ -122,10 +126,9 @@ class _CapturedRaggedDecode:
             self.logits = self._ops()
 
     def _ops(self) -> torch.Tensor:
-        r = self.runner
         self.tidx.copy_(self.tidx32)
-        r.b_req_tokens_table.view(-1).index_copy_(0, self.tidx, self.rows)
-        return r.model.forward(self.ids, self.batch, r.kv_buffer_of, r.b_req_tokens_table, r.state_manager, None)
+        self._table.view(-1).index_copy_(0, self.tidx, self.rows)
+        return self._model.forward(self.ids, self.batch, self._kv, self._table, self._states, None)
 
     def replay(self, packed_host: torch.Tensor) -> torch.Tensor:
         self.packed.copy_(packed_host, non_blocking=True)
