@@ -224,7 +224,8 @@ int b2l_moe_gemm(void* c, const void* a, const void* w, int weight_kind, const v
                  int num_experts, int64_t n, int64_t k, int64_t a_row_stride, int64_t w_row_stride,
                  int64_t c_row_stride, int64_t group_n, int64_t group_k, int64_t s_stride_e, int64_t s_stride_n,
                  int64_t s_stride_k, void* stream);
-int b2l_moe_sum(void* out, const void* in, int64_t tokens, int64_t n, int top_k, int dtype, void* stream);
+int b2l_moe_sum(void* out, const void* in, const void* addend, int64_t tokens, int64_t n, int top_k, int dtype,
+                void* stream);
 /* Router (lite_llama/models/qwen3_moe.py:94-100): fp32 softmax over all experts of the [tokens, E] logits,
  * top-k (ties -> lowest index), optional renormalisation; weights in the activation dtype, ids int64. */
 int b2l_moe_route_topk(void* topk_weights, void* topk_ids_i64, const void* router_logits, int64_t row_stride,
@@ -262,17 +263,58 @@ int b2l_tp_allreduce_skip_rmsnorm(int64_t comm, void* y, const void* x_partial, 
 int b2l_gemm_simt(void* y, const void* x, const void* w, const void* bias, int64_t m, int64_t n, int64_t k,
                   int64_t x_row_stride, int64_t w_row_stride, int64_t y_row_stride, int dtype, void* stream);
 
-/* residual[t] = embed[token[t]] + pos_table[pos[t]] (pos_table nullable); act (nullable) gets the copy in dtype. */
+/* Norm kinds of the entry points below: 0 = RMS (x / sqrt(mean(x^2) + eps)), 1 = layer norm without bias
+ * ((x - mean) / sqrt(mean((x - mean)^2) + eps)). */
+/* residual[t] = scale * embed[token[t]] + pos_table[pos[t]] (pos_table nullable); act (nullable) gets the copy in dtype. */
 int b2l_embed_positions(void* residual_f32, void* act, const void* tokens_i32, const void* pos_i32, const void* embed,
-                        const void* pos_table, int64_t rows, int64_t n, int64_t vocab, int64_t max_pos, int dtype,
-                        void* stream);
-/* residual += y / sqrt(mean(y^2) + eps) * (weight_offset + weight): the norm sits on the sublayer OUTPUT. */
-int b2l_post_norm_residual(void* residual_f32, void* act, const void* y, const void* weight, int64_t rows, int64_t n,
-                           int64_t y_row_stride, float eps, float weight_offset, int dtype, void* stream);
-/* out[i] = rmsnorm(residual[rows[i]]) * (weight_offset + weight); rows_i32 nullable = identity. */
+                        const void* pos_table, int64_t rows, int64_t n, int64_t vocab, int64_t max_pos, float scale,
+                        int dtype, void* stream);
+/* residual += norm(y) * (weight_offset + weight) * layer_scale (nullable): the norm sits on the sublayer OUTPUT.
+ * act (nullable) gets the updated residual in dtype, or, with next_weight, the NEXT sublayer's input norm of it:
+ * norm'(residual) * next_weight (kind next_norm_kind). */
+int b2l_post_norm_residual(void* residual_f32, void* act, const void* y, const void* weight, const void* layer_scale,
+                           const void* next_weight, int64_t rows, int64_t n, int64_t y_row_stride, float eps,
+                           float weight_offset, int norm_kind, int next_norm_kind, int dtype, void* stream);
+/* out[i] = norm(residual[rows[i]]) * (weight_offset + weight); rows_i32 nullable = identity. */
 int b2l_rmsnorm_from_f32(void* out, const void* residual_f32, const void* rows_i32, const void* weight, int64_t rows,
-                         int64_t n, float eps, float weight_offset, int dtype, void* stream);
+                         int64_t n, float eps, float weight_offset, int norm_kind, int dtype, void* stream);
 int b2l_relu_squared(void* out, const void* x, int64_t total, int dtype, void* stream);
+/* out = gelu(x): exact (erf) form, or the tanh form 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))). */
+int b2l_gelu(void* out, const void* x, int64_t total, int tanh_form, int dtype, void* stream);
+/* out_f32 = cap * tanh(x / cap) (cap <= 0: x) as fp32: soft-capped logits. */
+int b2l_softcap_to_f32(void* out_f32, const void* x, int64_t total, float cap, int dtype, void* stream);
+/* y[t, h, :] = W[h] . x[t, h, :] for W [heads, n, k] (csrc/gemm_simt.cu); x / y rows hold the heads side by side
+ * (strides in elements); gate (nullable) [m, >= heads]: y[t, h, :] *= sigmoid(gate[t, h]). */
+int b2l_head_linear(void* y, int64_t y_row_stride, int64_t y_head_stride, const void* x, int64_t x_row_stride,
+                    int64_t x_head_stride, const void* w, const void* gate, int64_t gate_row_stride, int64_t m,
+                    int heads, int64_t n, int64_t k, int dtype, void* stream);
+/* Grouped product over expert-sorted slots (b2l_moe_align_block_size with block_size = b2l_moe_gemm_simt_block()):
+ * c[s, :] = act(W[expert(s)] . a[s / top_k, :]) * slot_weight_f32[s] (nullable); act 0 = none, 1 = exact gelu;
+ * W [experts, n, k] dense; every dtype of this section, fp32 sums in ascending k. */
+int b2l_moe_gemm_simt_block(void);
+int b2l_moe_gemm_simt(void* c, const void* a, const void* w, const void* slot_weight_f32,
+                      const void* sorted_token_ids, const void* expert_ids, const void* num_tokens_post_padded,
+                      int64_t em, int64_t num_valid_slots, int top_k, int64_t n, int64_t k, int64_t a_row_stride,
+                      int64_t c_row_stride, int act, int dtype, void* stream);
+/* Router product + sigmoid scores + selection bias + group-limited top-k in one launch (csrc/moe_routing.cu):
+ * z = router_w . x in fp32, s = sigmoid(z), choice = s + bias (nullable); `groups` equal runs of neighbouring experts,
+ * group score = sum of its two largest choice scores, only the `keep` best groups are eligible; the top_k largest
+ * choice scores win; weights_f32 [tokens, top_k] = s of the winners / (their sum + 1e-20); ids_i32 [tokens, top_k]. */
+int b2l_moe_route_sigmoid_groups(void* weights_f32, void* ids_i32, const void* x, int64_t x_row_stride,
+                                 const void* router_w, const void* bias, int64_t tokens, int num_experts, int64_t k,
+                                 int top_k, int groups, int keep, int dtype, void* stream);
+/* Latent attention, per token of the fused down-projection row [a: q_rank | b: kv_rank | r: rot_dim | ...]
+ * (csrc/latent_attention.cu): a <- rmsnorm(a) * q_norm_weight in place; pool row kv_rows[t] =
+ * [rmsnorm(b) * kv_norm_weight | r with its first rot_dims entries rotated by pos[t]]. */
+int b2l_latent_prepare(void* proj, int64_t proj_row_stride, void* pool, int64_t pool_row_stride,
+                       const void* kv_rows_i32, const void* pos_i32, const void* q_norm_weight,
+                       const void* kv_norm_weight, int64_t tokens, int q_rank, int kv_rank, int rot_dim, int rot_dims,
+                       float rot_base, float eps, int dtype, void* stream);
+/* dst[t, h, :width] = src[t, h, :width], the first rot_dims entries rotated by pos[t] (entry i pairs with
+ * i + rot_dims / 2, angle pos * base^(-2i / rot_dims)). */
+int b2l_rope_heads(void* dst, int64_t dst_row_stride, int dst_head_stride, const void* src, int64_t src_row_stride,
+                   int src_head_stride, const void* pos_i32, int64_t tokens, int heads, int width, int rot_dims,
+                   float rot_base, int dtype, void* stream);
 
 /* Short causal convolution per channel + SiLU over a ragged step, and the slot's tail (last taps-1 inputs) update.
  * in: [tokens, >= channels] with row stride; weight [channels, taps] (last column = current token); tail
@@ -300,14 +342,16 @@ int b2l_attn_prepare(void* qkv, int64_t qkv_row_stride, void* kv_pool, int64_t k
                      float eps, float gain_coef, float gain_every, int dtype, void* stream);
 /* Soft-capped attention with an optional per-head sink over the pool (csrc/attention_sink.cu).  num_splits == 0: tiled
  * mode for sequences of up to max_q_len new tokens; num_splits > 0: every listed sequence brings one token, its keys
- * are cut into num_splits ranges of split_keys and merged (workspace: b2l_sink_attention_workspace_bytes). */
+ * (from the first one it sees) are cut into num_splits ranges of split_keys and merged (workspace:
+ * b2l_sink_attention_workspace_bytes).  window > 0: token p sees keys p - window + 1 .. p only.  v_col0 < 0: a pool
+ * row is [keys | values]; v_col0 >= 0: the values start at that column (0: they are the keys' leading columns). */
 int64_t b2l_sink_attention_workspace_bytes(int64_t num_seqs, int heads, int v_head_dim, int num_splits);
 int b2l_sink_attention(void* out, int64_t out_row_stride, const void* q, int64_t q_row_stride, const void* kv_pool,
                        int64_t kv_row_stride, const void* table_i32, int64_t table_row_stride, const void* seq_start,
                        const void* seq_ctx, const void* seq_slot, const void* seq_list, int64_t num_seqs,
                        int max_q_len, const void* sink, int heads, int kv_heads, int head_dim, int v_head_dim,
-                       float scale, float softcap, int num_splits, int split_keys, void* workspace,
-                       int64_t workspace_bytes, int dtype, void* stream);
+                       float scale, float softcap, int window, int v_col0, int num_splits, int split_keys,
+                       void* workspace, int64_t workspace_bytes, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

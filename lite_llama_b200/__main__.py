@@ -44,7 +44,9 @@ def main(argv: list[str] | None = None) -> int:
     if a.cmd == "build":
         build(verbose=True)
         return 0
-    build(verbose=False, sources=LAYERED_SOURCES)      # checkpoint directories hold layer-list models
+    from .executor.registry import architecture_of
+
+    build(verbose=False, sources=architecture_of(a.model)[0].sources or LAYERED_SOURCES)    # what this family launches
     if a.cmd == "trace":
         from .trace import replay
 

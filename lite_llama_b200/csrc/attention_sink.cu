@@ -1,7 +1,10 @@
 // Attention over the token-granular KV pool for RAGGED steps, with the score shaping of the sink / soft-cap family:
 //   score = softcap * tanh(q.k * scale / softcap)   (softcap <= 0: plain q.k * scale)
 //   p_j   = exp(score_j) / (sum_i exp(score_i) + exp(sink_h))      (sink == NULL: ordinary softmax)
-// K and V rows may have different head sizes (D, Dv): a pool row is [G*D keys | G*Dv values].
+// K and V rows may have different head sizes (D, Dv): a pool row is [G*D keys | G*Dv values]; the values may instead
+// start at any column `v_col0` of the row (v_col0 = 0: the values ARE the leading Dv columns of the keys, which is
+// how a latent cache [latent | rotated key part] is read by queries that were multiplied into the latent space).
+// A sliding window (`window` > 0) limits token p to the keys p - window + 1 .. p.
 //
 //   attn_prepare   per token: whole-row RMS norm of q and of k (one statistic over ALL heads, plain weight),
 //                  position-dependent query gain, value mixing with an earlier layer's values, K|V cache write
@@ -32,6 +35,7 @@ struct AttnArgs {
   void* out; int64_t out_stride;
   float* part;
   int H, G, D, Dv, PH, BQ, nsplit, chunk;
+  int window, v_col0;          // window <= 0: every earlier key is visible; v_col0: first value column of a pool row
   float scale, softcap;
 };
 
@@ -53,7 +57,8 @@ __global__ void __launch_bounds__(kWarps * 32) sink_attention_kernel(AttnArgs a)
   const int t0 = blockIdx.x * a.BQ;
   if (t0 >= qlen) return;
   const int t_count = min(a.BQ, qlen - t0);
-  const int key_lo = 0, key_hi = ctx + t0 + t_count;    // exclusive
+  const int key_hi = ctx + t0 + t_count;                // exclusive
+  const int key_lo = a.window > 0 ? max(0, ctx + t0 - a.window + 1) : 0;      // first key the tile's first token sees
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const T* q = (const T*)a.q;
   const T* kv = (const T*)a.kv;
@@ -85,7 +90,7 @@ __global__ void __launch_bounds__(kWarps * 32) sink_attention_kernel(AttnArgs a)
     }
     for (int i = tid; i < kKeys * Dv; i += blockDim.x) {
       const int j = i / Dv, d = i - j * Dv;
-      vs[i] = j < nk ? to_f32(kv[(int64_t)trow[k0 + j] * a.kv_stride + a.G * D + g * Dv + d]) : 0.f;
+      vs[i] = j < nk ? to_f32(kv[(int64_t)trow[k0 + j] * a.kv_stride + a.v_col0 + g * Dv + d]) : 0.f;
     }
     __syncthreads();
     float sc[kRowsPerWarp];
@@ -101,9 +106,11 @@ __global__ void __launch_bounds__(kWarps * 32) sink_attention_kernel(AttnArgs a)
 #pragma unroll
     for (int i = 0; i < kRowsPerWarp; ++i) {
       if (row_pos[i] < k0) continue;              // warp-uniform: nothing visible in this tile (or unused row)
+      const int row_lo = a.window > 0 ? row_pos[i] - a.window + 1 : 0;
+      if (row_lo >= k0 + nk) continue;            // warp-uniform: the row's window starts after this tile
       float sv = sc[i] * a.scale;
       if (a.softcap > 0.f) sv = a.softcap * tanhf(sv * inv_cap);
-      const bool ok = lane < nk && k0 + lane <= row_pos[i];
+      const bool ok = lane < nk && k0 + lane <= row_pos[i] && k0 + lane >= row_lo;
       sv = ok ? sv : -INFINITY;
       const float mt = warp_reduce_max(sv);
       const float mn = fmaxf(m[i], mt);
@@ -191,6 +198,10 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(AttnArgs a) {
   const int r0 = warp * 16 + gq, r1 = r0 + 8;                    // rows of the tile
   const bool ok0 = r0 < t_count, ok1 = r1 < t_count;
   const int pos0 = ctx + t0 + r0, pos1 = ctx + t0 + r1;          // last visible key of each row
+  const int lo0 = a.window > 0 ? pos0 - a.window + 1 : 0, lo1 = a.window > 0 ? pos1 - a.window + 1 : 0;   // first one
+  // first key tile: the one that holds the first key of the tile's first token (tiles stay aligned to kTileN)
+  const int k_first = a.window > 0 ? max(0, ctx + t0 - a.window + 1) / kTileN * kTileN : 0;
+  const int warp_first = a.window > 0 ? ctx + t0 + warp * 16 - a.window + 1 : 0;      // first key of the warp's rows
   const T* q = (const T*)a.q;
   const T* kv = (const T*)a.kv;
   uint32_t qf[DP / 16][4];
@@ -243,21 +254,21 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(AttnArgs a) {
     for (int j = 0; j < JV; ++j) {
       const int i = tid + 128 * j, r = i / (DVP / 8), c = (i - r * (DVP / 8)) * 8;
       if (rv[j] >= 0 && c < Dv)
-        cp_async_16(smem_u32(vdst + r * VP + c * 2), kv + (int64_t)rv[j] * a.kv_stride + a.G * D + g * Dv + c);
+        cp_async_16(smem_u32(vdst + r * VP + c * 2), kv + (int64_t)rv[j] * a.kv_stride + a.v_col0 + g * Dv + c);
       else
         *reinterpret_cast<uint4*>(vdst + r * VP + c * 2) = make_uint4(0u, 0u, 0u, 0u);
     }
     cp_async_commit();
   };
-  issue(0, 0);
-  for (int k0 = 0, it = 0; k0 < key_hi; k0 += kTileN, ++it) {
+  issue(k_first, 0);
+  for (int k0 = k_first, it = 0; k0 < key_hi; k0 += kTileN, ++it) {
     const bool more = k0 + kTileN < key_hi;
     if (more) issue(k0 + kTileN, (it + 1) & 1);                  // the next tile flies while this one is used
     if (more) cp_async_wait<1>(); else cp_async_wait<0>();
     __syncthreads();                                             // tile `it` is complete and visible to every warp
     const uint32_t ks = smem_u32(smem_raw + (it & 1) * kStage), vs = ks + kTileN * KP;
     // the barrier at the END of the body keeps stage it & 1 intact until every warp is done with it
-    if (k0 > warp_last) { __syncthreads(); continue; }
+    if (k0 > warp_last || k0 + kTileN <= warp_first) { __syncthreads(); continue; }
     float sc[kTileN / 8][4];
 #pragma unroll
     for (int j = 0; j < kTileN / 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
@@ -281,10 +292,10 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(AttnArgs a) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int key = k0 + j * 8 + 2 * tq + (e & 1);
-        const int lim = (e >> 1) ? pos1 : pos0;
+        const int lim = (e >> 1) ? pos1 : pos0, first = (e >> 1) ? lo1 : lo0;
         float v = sc[j][e] * a.scale;
         if (cap > 0.f) v = cap * tanh_fast(v * inv_cap);
-        v = key <= lim ? v * kLog2e : -INFINITY;
+        v = (key <= lim && key >= first) ? v * kLog2e : -INFINITY;
         sc[j][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
       }
@@ -393,7 +404,7 @@ int dispatch_attention_mma(const AttnArgs& a, int max_q_len, int64_t num_seqs, c
 inline bool mma_path_ok(const AttnArgs& a, int dtype) {
   if (dtype != B2L_F16 && dtype != B2L_BF16) return false;
   if (a.D % 8 || a.Dv % 8 || a.D > 128 || a.Dv > 128) return false;
-  if (a.kv_stride % 8 || a.q_stride % 2 || a.out_stride % 2) return false;
+  if (a.kv_stride % 8 || a.v_col0 % 8 || a.q_stride % 2 || a.out_stride % 2) return false;
   if (((uintptr_t)a.kv % 16) || ((uintptr_t)a.q % 4) || ((uintptr_t)a.out % 4)) return false;
   return true;
 }
@@ -426,7 +437,8 @@ __global__ void __launch_bounds__(128) sink_attention_split_kernel(AttnArgs a) {
   const int hchunks = (per + kSplitRows - 1) / kSplitRows;
   const int g = blockIdx.y / hchunks, h_first = g * per + (blockIdx.y % hchunks) * kSplitRows;
   const int h_count = min(kSplitRows, g * per + per - h_first);
-  const int key_lo = blockIdx.x * a.chunk, key_hi = min(key_lo + a.chunk, ctx + 1);
+  const int win_lo = a.window > 0 ? max(0, ctx - a.window + 1) : 0;          // the new token's first visible key
+  const int key_lo = win_lo + blockIdx.x * a.chunk, key_hi = min(key_lo + a.chunk, ctx + 1);
   const T* q = (const T*)a.q;
   const T* kv = (const T*)a.kv;
   const int Dq = (D + 3) / 4 * 4;
@@ -444,7 +456,8 @@ __global__ void __launch_bounds__(128) sink_attention_split_kernel(AttnArgs a) {
   }
   const int* trow = a.table + slot * a.table_stride;
   const float inv_cap = a.softcap > 0.f ? 1.0f / a.softcap : 0.f;
-  const bool vec_ok = (D % VEC == 0) && (Dv % VEC == 0) && (a.kv_stride % VEC == 0) && (((uintptr_t)a.kv % 16) == 0);
+  const bool vec_ok = (D % VEC == 0) && (Dv % VEC == 0) && (a.kv_stride % VEC == 0) && (a.v_col0 % VEC == 0) &&
+                      (((uintptr_t)a.kv % 16) == 0);
   for (int k0 = key_lo + warp * 32; k0 < key_hi; k0 += 128) {
     const int nk = min(32, key_hi - k0);
     __syncwarp();
@@ -470,7 +483,7 @@ __global__ void __launch_bounds__(128) sink_attention_split_kernel(AttnArgs a) {
         }
       };
       stage_rows(ks, Dp, g * D, D / VEC);
-      stage_rows(vs, Dvp, a.G * D + g * Dv, Dv / VEC);
+      stage_rows(vs, Dvp, a.v_col0 + g * Dv, Dv / VEC);
     } else {
       for (int i = lane; i < nk * D; i += 32) {
         const int j = i / D, d = i - j * D;
@@ -478,7 +491,7 @@ __global__ void __launch_bounds__(128) sink_attention_split_kernel(AttnArgs a) {
       }
       for (int i = lane; i < nk * Dv; i += 32) {
         const int j = i / Dv, d = i - j * Dv;
-        vs[j * Dvp + d] = kv[(int64_t)trow[k0 + j] * a.kv_stride + a.G * D + g * Dv + d];
+        vs[j * Dvp + d] = kv[(int64_t)trow[k0 + j] * a.kv_stride + a.v_col0 + g * Dv + d];
       }
     }
     __syncwarp();
@@ -819,14 +832,16 @@ extern "C" int64_t b2l_sink_attention_workspace_bytes(int64_t num_seqs, int head
 }
 
 /* num_splits == 0: tiled mode over `max_q_len`-token sequences; > 0: split mode, every listed sequence brings ONE token
- * and `split_keys` keys go to each of the num_splits ranges (num_splits * split_keys >= longest context + 1). */
+ * and `split_keys` keys go to each of the num_splits ranges, counted from the token's first visible key
+ * (num_splits * split_keys >= the most keys any listed token sees: context + 1, or the window if that is smaller).
+ * window <= 0: no sliding window; v_col0 < 0: the values follow the keys in a pool row (column kv_heads * head_dim). */
 extern "C" int b2l_sink_attention(void* out, int64_t out_row_stride, const void* q, int64_t q_row_stride,
                                   const void* kv_pool, int64_t kv_row_stride, const void* table_i32,
                                   int64_t table_row_stride, const void* seq_start, const void* seq_ctx,
                                   const void* seq_slot, const void* seq_list, int64_t num_seqs, int max_q_len,
                                   const void* sink, int heads, int kv_heads, int head_dim, int v_head_dim, float scale,
-                                  float softcap, int num_splits, int split_keys, void* workspace,
-                                  int64_t workspace_bytes, int dtype, void* stream) {
+                                  float softcap, int window, int v_col0, int num_splits, int split_keys,
+                                  void* workspace, int64_t workspace_bytes, int dtype, void* stream) {
   B2L_REQUIRE(out && q && kv_pool && table_i32 && seq_start && seq_ctx && seq_slot, "sink_attention: null pointer");
   B2L_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "sink_attention: %d heads must be a multiple of num_kv_heads %d",
               heads, kv_heads);
@@ -844,6 +859,8 @@ extern "C" int b2l_sink_attention(void* out, int64_t out_row_stride, const void*
   a.PH = per < kRows ? per : kRows;
   a.BQ = kRows / a.PH;
   a.nsplit = num_splits; a.chunk = split_keys; a.scale = scale; a.softcap = softcap;
+  a.window = window > 0 ? window : 0;
+  a.v_col0 = v_col0 >= 0 ? v_col0 : kv_heads * head_dim;
   const int hchunks = (per + a.PH - 1) / a.PH;
   if (num_splits > 0) {
     B2L_REQUIRE(split_keys > 0, "sink_attention: split_keys must be positive");

@@ -772,10 +772,12 @@ extern "C" int b2l_skip_rmsnorm_quant_int8(void* q, void* scales, const void* x,
 
 // --------------------------------------------------------------------------- //
 // moe_sum (reference: lite_llama/kernels/fused_moe.py:316-333)
-//   out[m, :] = sum_k in[m*top_k + k, :]   (fp32 accumulate, in slot order)
+//   out[m, :] = sum_k in[m*top_k + k, :] (+ addend[m, :])   (fp32 accumulate, in slot order; the addend, e.g. a
+//   shared expert's output, joins last)
 // --------------------------------------------------------------------------- //
 template <typename T>
-__global__ void moe_sum_kernel(T* __restrict__ out, const T* __restrict__ in, int64_t tokens, int64_t n, int top_k) {
+__global__ void moe_sum_kernel(T* __restrict__ out, const T* __restrict__ in, const T* __restrict__ addend,
+                               int64_t tokens, int64_t n, int top_k) {
   pdl_prologue();
   // grid.y is capped at 65535: tokens are swept with a grid stride (MoE prefill can exceed the cap)
   for (int64_t m = blockIdx.y; m < tokens; m += gridDim.y) {
@@ -783,22 +785,22 @@ __global__ void moe_sum_kernel(T* __restrict__ out, const T* __restrict__ in, in
       float acc = 0.f;
       const T* base = in + m * top_k * n + c;
       for (int i = 0; i < top_k; ++i) acc += to_f32(base[(int64_t)i * n]);
+      if (addend) acc += to_f32(addend[m * n + c]);
       out[m * n + c] = from_f32<T>(acc);
     }
   }
 }
 
-extern "C" int b2l_moe_sum(void* out, const void* in, int64_t tokens, int64_t n, int top_k, int dtype, void* stream) {
+extern "C" int b2l_moe_sum(void* out, const void* in, const void* addend, int64_t tokens, int64_t n, int top_k,
+                           int dtype, void* stream) {
   B2L_REQUIRE(out && in, "moe_sum: null pointer");
   if (tokens == 0 || n == 0) return B2L_OK;
   dim3 grid((unsigned)cdiv64(n, 256), (unsigned)(tokens > 65535 ? 65535 : tokens));
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == B2L_F16)
-    b2l_launch(moe_sum_kernel<__half>, dim3(grid), dim3(256), (size_t)(0), st, (__half*)out, (const __half*)in, tokens, n, top_k);
-  else if (dtype == B2L_BF16)
-    b2l_launch(moe_sum_kernel<__nv_bfloat16>, dim3(grid), dim3(256), (size_t)(0), st, (__nv_bfloat16*)out, (const __nv_bfloat16*)in, tokens, n, top_k);
-  else
-    B2L_UNSUPPORTED("moe_sum: dtype %d", dtype);
+  B2L_DISPATCH_FLOAT(dtype, "moe_sum", {
+    b2l_launch(moe_sum_kernel<T>, dim3(grid), dim3(256), (size_t)(0), st, (T*)out, (const T*)in, (const T*)addend,
+               tokens, n, top_k);
+  });
   B2L_LAUNCH_CHECK();
   return B2L_OK;
 }

@@ -1,0 +1,133 @@
+// Per-token preparation for LATENT attention: queries and keys/values go through low-rank latents, only the key/value
+// latent and one rotated key part shared by all heads are cached, and the queries are multiplied into the latent space
+// so that attention runs directly on the cached rows (csrc/attention_sink.cu with one kv head, value columns =
+// the latent itself):
+//
+//   proj row  = [ a: q_rank | b: kv_rank | r: rot_dim | ... ]          (one fused down-projection of the mixer input)
+//   a  <- a / rms(a) * wq                in place: the input of the query up-projection
+//   pool row  = [ b / rms(b) * wkv | rotate(r, pos) ]
+//
+//   rope_heads: dst[t, h, :width] = src[t, h, :width] with the first `rot_dims` entries rotated by the token's position
+//               (entry i pairs with entry i + rot_dims/2; angle pos * base^(-2i/rot_dims)); the rest is copied.
+//
+// Statistics and the rotation are fp32; the angle and its sine / cosine are evaluated in fp64 (a position of a few
+// thousand times a frequency near 1 loses the low bits of the angle in fp32).
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float block_sum_l(float v, float* red) {
+  v = warp_reduce_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.f;
+  t = warp_reduce_sum(t);
+  __syncthreads();
+  return t;
+}
+
+// cos / sin of pos * base^(-2i/dims) for pair i
+__device__ __forceinline__ void pair_angle(int pos, int i, int dims, double log2_base, float& c, float& s) {
+  const double f = exp2(-2.0 * (double)i / (double)dims * log2_base);
+  double sd, cd;
+  sincos((double)pos * f, &sd, &cd);
+  c = (float)cd; s = (float)sd;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) latent_prepare_kernel(T* __restrict__ proj, int64_t stride, T* __restrict__ pool,
+                                                             int64_t pool_stride, const int* __restrict__ rows,
+                                                             const int* __restrict__ pos, const T* __restrict__ wq,
+                                                             const T* __restrict__ wkv, int q_rank, int kv_rank,
+                                                             int rot_dim, int rot_dims, double log2_base, float eps) {
+  pdl_prologue();
+  __shared__ float red[32];
+  const int64_t t = blockIdx.x;
+  T* a = proj + t * stride;
+  const T* b = a + q_rank;
+  const T* r = b + kv_rank;
+  T* dst = pool + (int64_t)rows[t] * pool_stride;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < q_rank; i += blockDim.x) { const float v = to_f32(a[i]); ss = fmaf(v, v, ss); }
+  float rstd = 1.0f / sqrtf(block_sum_l(ss, red) / (float)q_rank + eps);
+  for (int i = threadIdx.x; i < q_rank; i += blockDim.x) a[i] = from_f32<T>(to_f32(a[i]) * rstd * to_f32(wq[i]));
+  ss = 0.f;
+  for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) { const float v = to_f32(b[i]); ss = fmaf(v, v, ss); }
+  rstd = 1.0f / sqrtf(block_sum_l(ss, red) / (float)kv_rank + eps);
+  for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) dst[i] = from_f32<T>(to_f32(b[i]) * rstd * to_f32(wkv[i]));
+  const int half = rot_dims / 2, p = pos[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float c, s;
+    pair_angle(p, i, rot_dims, log2_base, c, s);
+    const float u = to_f32(r[i]), v = to_f32(r[i + half]);
+    dst[kv_rank + i] = from_f32<T>(u * c - v * s);
+    dst[kv_rank + i + half] = from_f32<T>(v * c + u * s);
+  }
+  for (int i = 2 * half + threadIdx.x; i < rot_dim; i += blockDim.x) dst[kv_rank + i] = r[i];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) rope_heads_kernel(T* __restrict__ dst, int64_t dst_stride, int dst_head_stride,
+                                                         const T* __restrict__ src, int64_t src_stride,
+                                                         int src_head_stride, const int* __restrict__ pos, int heads,
+                                                         int width, int rot_dims, double log2_base) {
+  pdl_prologue();
+  extern __shared__ float cs[];                      // [half] cos, [half] sin of this token
+  const int64_t t = blockIdx.x;
+  const int half = rot_dims / 2, p = pos[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) pair_angle(p, i, rot_dims, log2_base, cs[i], cs[half + i]);
+  __syncthreads();
+  const T* s = src + t * src_stride;
+  T* d = dst + t * dst_stride;
+  for (int i = threadIdx.x; i < heads * width; i += blockDim.x) {
+    const int h = i / width, c = i - h * width;
+    const T* sh = s + (int64_t)h * src_head_stride;
+    float v;
+    if (c < half) v = to_f32(sh[c]) * cs[c] - to_f32(sh[c + half]) * cs[half + c];
+    else if (c < 2 * half) v = to_f32(sh[c]) * cs[c - half] + to_f32(sh[c - half]) * cs[c];
+    else v = to_f32(sh[c]);
+    d[(int64_t)h * dst_head_stride + c] = from_f32<T>(v);
+  }
+}
+
+}  // namespace
+
+extern "C" int b2l_latent_prepare(void* proj, int64_t proj_row_stride, void* pool, int64_t pool_row_stride,
+                                  const void* kv_rows_i32, const void* pos_i32, const void* q_norm_weight,
+                                  const void* kv_norm_weight, int64_t tokens, int q_rank, int kv_rank, int rot_dim,
+                                  int rot_dims, float rot_base, float eps, int dtype, void* stream) {
+  B2L_REQUIRE(proj && pool && kv_rows_i32 && pos_i32 && q_norm_weight && kv_norm_weight, "latent_prepare: null pointer");
+  B2L_REQUIRE(q_rank > 0 && kv_rank > 0 && rot_dim >= 0 && rot_dims >= 0 && rot_dims <= rot_dim && rot_dims % 2 == 0,
+              "latent_prepare: bad shape (q_rank %d, kv_rank %d, rot_dim %d, rot_dims %d)", q_rank, kv_rank, rot_dim, rot_dims);
+  B2L_REQUIRE(rot_base > 0.f, "latent_prepare: rotary base must be positive");
+  if (tokens <= 0) return B2L_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const double l2b = log2((double)rot_base);
+  B2L_DISPATCH_FLOAT(dtype, "latent_prepare", {
+    b2l_launch(latent_prepare_kernel<T>, dim3((unsigned)tokens), dim3(128), (size_t)0, st, (T*)proj, proj_row_stride,
+               (T*)pool, pool_row_stride, (const int*)kv_rows_i32, (const int*)pos_i32, (const T*)q_norm_weight,
+               (const T*)kv_norm_weight, q_rank, kv_rank, rot_dim, rot_dims, l2b, eps);
+  });
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}
+
+extern "C" int b2l_rope_heads(void* dst, int64_t dst_row_stride, int dst_head_stride, const void* src,
+                              int64_t src_row_stride, int src_head_stride, const void* pos_i32, int64_t tokens,
+                              int heads, int width, int rot_dims, float rot_base, int dtype, void* stream) {
+  B2L_REQUIRE(dst && src && pos_i32, "rope_heads: null pointer");
+  B2L_REQUIRE(heads > 0 && width >= 0 && rot_dims >= 0 && rot_dims <= width && rot_dims % 2 == 0 && rot_base > 0.f,
+              "rope_heads: bad shape (heads %d, width %d, rot_dims %d)", heads, width, rot_dims);
+  if (tokens <= 0 || width == 0) return B2L_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const double l2b = log2((double)rot_base);
+  const size_t smem = (size_t)(rot_dims > 0 ? rot_dims : 1) * sizeof(float);
+  B2L_DISPATCH_FLOAT(dtype, "rope_heads", {
+    b2l_launch(rope_heads_kernel<T>, dim3((unsigned)tokens), dim3(128), smem, st, (T*)dst, dst_row_stride,
+               dst_head_stride, (const T*)src, src_row_stride, src_head_stride, (const int*)pos_i32, heads, width,
+               rot_dims, l2b);
+  });
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}

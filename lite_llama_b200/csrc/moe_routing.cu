@@ -140,6 +140,100 @@ __global__ void moe_route_kernel(const T* __restrict__ logits, int64_t row_strid
   }
 }
 
+// Sigmoid router with a selection bias and group-limited choice, router product included (one CTA per token):
+//   z = W_r . x (fp32 sums),  s = sigmoid(z),  choice = s + bias
+//   the experts form `groups` equal runs of neighbours; a group's score = the sum of its two largest choice scores;
+//   only experts of the `keep` best groups can be chosen; the `top_k` largest choice scores among them win
+//   (lowest index on ties); weights = s of the winners / (their sum + 1e-20), fp32.
+template <typename T>
+__global__ void __launch_bounds__(128) moe_route_sigmoid_kernel(const T* __restrict__ x, int64_t xs,
+                                                                const T* __restrict__ wr, const T* __restrict__ bias,
+                                                                int num_experts, int k, int top_k, int groups, int keep,
+                                                                float* __restrict__ out_w, int* __restrict__ out_ids) {
+  pdl_prologue();
+  extern __shared__ float rs[];
+  float* sc = rs;                                // [E] sigmoid scores
+  float* ch = sc + num_experts;                  // [E] choice scores; -inf once taken or outside the kept groups
+  float* gs = ch + num_experts;                  // [groups]
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const T* xr = x + (int64_t)t * xs;
+  for (int e = warp; e < num_experts; e += nw) {
+    const T* w = wr + (int64_t)e * k;
+    float acc = 0.f;
+    for (int i = lane; i < k; i += 32) acc = fmaf(to_f32(xr[i]), to_f32(w[i]), acc);
+    acc = warp_reduce_sum(acc);
+    if (lane == 0) {
+      const float s = 1.0f / (1.0f + expf(-acc));
+      sc[e] = s;
+      ch[e] = s + (bias ? to_f32(bias[e]) : 0.f);
+    }
+  }
+  __syncthreads();
+  const int per = num_experts / groups;
+  for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+    float a = -INFINITY, b = -INFINITY;          // largest, second largest
+    for (int e = g * per; e < (g + 1) * per; ++e) {
+      const float v = ch[e];
+      if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+    }
+    gs[g] = per > 1 ? a + b : a;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  if (keep < groups) {
+    int* kept = reinterpret_cast<int*>(gs + groups);            // [groups]
+    for (int g = lane; g < groups; g += 32) kept[g] = 0;
+    __syncwarp();
+    for (int r = 0; r < keep; ++r) {                            // the best group not yet kept, lowest index on ties
+      float best = -INFINITY; int bi = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32) {
+        const float v = gs[g];
+        if (!kept[g] && (bi == 0x7fffffff || v > best)) { best = v; bi = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
+      }
+      if (lane == 0) kept[bi] = 1;
+      __syncwarp();
+    }
+    for (int e = lane; e < num_experts; e += 32)
+      if (!kept[e / per]) ch[e] = -INFINITY;
+    __syncwarp();
+  }
+  float total = 0.f, my_w = 0.f;
+  int my_id = 0;
+  for (int r = 0; r < top_k; ++r) {
+    float best = -INFINITY; int bi = 0x7fffffff;
+    for (int e = lane; e < num_experts; e += 32) {
+      const float v = ch[e];
+      if (v > best || (v == best && e < bi)) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (bi >= num_experts) bi = 0;               // fewer selectable experts than top_k: never happens for valid configs
+    const float s = sc[bi];
+    total += s;
+    if (lane == (r & 31)) { my_w = s; my_id = bi; }
+    __syncwarp();
+    if (lane == 0) ch[bi] = -INFINITY;
+    __syncwarp();
+    if ((r & 31) == 31 || r == top_k - 1) {      // flush up to 32 picks; the weights are normalised below
+      const int base = r & ~31;
+      if (base + lane <= r) { out_w[(int64_t)t * top_k + base + lane] = my_w; out_ids[(int64_t)t * top_k + base + lane] = my_id; }
+    }
+  }
+  __syncwarp();
+  const float inv = 1.0f / (total + 1e-20f);
+  for (int r = lane; r < top_k; r += 32) out_w[(int64_t)t * top_k + r] *= inv;
+}
+
 }  // namespace
 
 extern "C" int b2l_moe_align_block_size(const void* topk_ids, int id_width, int64_t num_slots, int block_size,
@@ -188,6 +282,30 @@ extern "C" int b2l_moe_route_topk(void* topk_weights, void* topk_ids_i64, const 
   else B2L_UNSUPPORTED("moe_route_topk: dtype %d", dtype);
 #undef ROUTE_DISPATCH
 #undef ROUTE_LAUNCH
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}
+
+/* Router product + sigmoid scores + selection bias + group-limited top-k in one launch (fp32 throughout):
+ * x [tokens, k] and router_w [experts, k] in dtype, bias [experts] in dtype (nullable); weights_f32 [tokens, top_k],
+ * ids_i32 [tokens, top_k].  groups must divide experts; keep <= groups. */
+extern "C" int b2l_moe_route_sigmoid_groups(void* weights_f32, void* ids_i32, const void* x, int64_t x_row_stride,
+                                            const void* router_w, const void* bias, int64_t tokens, int num_experts,
+                                            int64_t k, int top_k, int groups, int keep, int dtype, void* stream) {
+  B2L_REQUIRE(weights_f32 && ids_i32 && x && router_w, "moe_route_sigmoid_groups: null pointer");
+  B2L_REQUIRE(num_experts > 0 && k > 0 && k < (1ll << 31) && top_k >= 1 && top_k <= num_experts && groups >= 1 &&
+                  num_experts % groups == 0 && keep >= 1 && keep <= groups &&
+                  (int64_t)keep * (num_experts / groups) >= top_k,
+              "moe_route_sigmoid_groups: %d experts, top %d, %d groups keep %d", num_experts, top_k, groups, keep);
+  if (tokens <= 0) return B2L_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t smem = (size_t)(2 * num_experts + 2 * groups) * sizeof(float);
+  B2L_REQUIRE(smem <= 48 * 1024, "moe_route_sigmoid_groups: %d experts exceed the kernel's shared memory", num_experts);
+  B2L_DISPATCH_FLOAT(dtype, "moe_route_sigmoid_groups", {
+    b2l_launch(moe_route_sigmoid_kernel<T>, dim3((unsigned)tokens), dim3(128), smem, st, (const T*)x, x_row_stride,
+               (const T*)router_w, (const T*)bias, num_experts, (int)k, top_k, groups, keep, (float*)weights_f32,
+               (int*)ids_i32);
+  });
   B2L_LAUNCH_CHECK();
   return B2L_OK;
 }

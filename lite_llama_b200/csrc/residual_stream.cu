@@ -1,9 +1,13 @@
 // Kernels around an fp32 residual stream (layer-list models: the residual sum stays in 32 bits while the
 // projections run in the activation dtype T):
-//   * embed_positions      r = embed[token] + position_table[pos]                       (+ copy in T for the next GEMM)
-//   * post_norm_residual   r += y / sqrt(mean(y^2) + eps) * (offset + w)                (norm on the SUBLAYER OUTPUT)
-//   * rmsnorm_from_f32     o = r / sqrt(mean(r^2) + eps) * (offset + w), selected rows  (final norm before the head)
-//   * relu_squared         o = max(x, 0)^2
+//   * embed_positions      r = scale * embed[token] + position_table[pos]               (+ copy in T for the next GEMM)
+//   * post_norm_residual   r += norm(y) * (offset + w) * layer_scale                    (norm on the SUBLAYER OUTPUT)
+//                          and, fused, the NEXT sublayer's input norm: act = norm'(r) * w'   (pre+post-norm designs)
+//   * rmsnorm_from_f32     o = norm(r) * (offset + w), selected rows                    (input norm / final norm)
+//   * relu_squared, gelu   o = max(x, 0)^2;  o = gelu(x), exact (erf) or tanh form
+//   * softcap_to_f32       o = cap * tanh(x / cap) as fp32 (cap <= 0: plain copy)       (logits)
+// norm = x / sqrt(mean(x^2) + eps) (kind 0, RMS) or (x - mean) / sqrt(mean((x - mean)^2) + eps) (kind 1, layer norm
+// without bias; the variance is taken from the deviations in a pass of its own).
 // `offset` = 1 for weights stored around zero, 0 for plain weights.  All statistics in fp32.
 #include "common.cuh"
 
@@ -23,7 +27,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 template <typename T>
 __global__ void embed_positions_kernel(float* __restrict__ r, T* __restrict__ act, const int* __restrict__ tokens,
                                        const int* __restrict__ pos, const T* __restrict__ embed,
-                                       const T* __restrict__ ptab, int64_t n, int64_t vocab, int64_t max_pos) {
+                                       const T* __restrict__ ptab, int64_t n, int64_t vocab, int64_t max_pos,
+                                       float scale) {
   pdl_prologue();
   const int64_t t = blockIdx.x;
   int64_t tok = tokens[t], p = pos[t];
@@ -31,44 +36,84 @@ __global__ void embed_positions_kernel(float* __restrict__ r, T* __restrict__ ac
   const bool has_pos = ptab != nullptr;
   p = p < 0 ? 0 : (p >= max_pos ? max_pos - 1 : p);
   for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
-    float v = to_f32(embed[tok * n + i]);
+    float v = to_f32(embed[tok * n + i]) * scale;
     if (has_pos) v += to_f32(ptab[p * n + i]);
     r[t * n + i] = v;
     if (act) act[t * n + i] = from_f32<T>(v);
   }
 }
 
+// (mean, 1 / sqrt(var + eps)) of row `x` under norm kind `kind`; every thread walks the same elements in every pass
+template <typename X>
+__device__ __forceinline__ void row_stats(const X* x, int64_t n, int kind, float eps, float* red, float& mean, float& rstd) {
+  mean = 0.f;
+  if (kind == 1) {
+    float s = 0.f;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) s += to_f32(x[i]);
+    mean = block_sum(s, red) / (float)n;
+  }
+  float ss = 0.f;
+  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) { const float v = to_f32(x[i]) - mean; ss = fmaf(v, v, ss); }
+  rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)n + eps);
+}
+
 template <typename T>
 __global__ void post_norm_residual_kernel(float* __restrict__ r, T* __restrict__ act, const T* __restrict__ y,
-                                          const T* __restrict__ w, int64_t n, int64_t ys, float eps, float offset) {
+                                          const T* __restrict__ w, const T* __restrict__ ls, const T* __restrict__ wn,
+                                          int64_t n, int64_t ys, float eps, float offset, int kind, int next_kind) {
   pdl_prologue();
   __shared__ float red[32];
   const int64_t t = blockIdx.x;
   const T* yr = y + t * ys;
-  float ss = 0.f;
-  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) { const float v = to_f32(yr[i]); ss = fmaf(v, v, ss); }
-  ss = block_sum(ss, red);
-  const float rr = 1.0f / sqrtf(ss / (float)n + eps);
+  float* rr = r + t * n;
+  float mean, rstd;
+  row_stats(yr, n, kind, eps, red, mean, rstd);
   for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = r[t * n + i] + to_f32(yr[i]) * rr * (offset + to_f32(w[i]));
-    r[t * n + i] = v;
-    if (act) act[t * n + i] = from_f32<T>(v);
+    float d = (to_f32(yr[i]) - mean) * rstd * (offset + to_f32(w[i]));
+    if (ls) d *= to_f32(ls[i]);
+    const float v = rr[i] + d;
+    rr[i] = v;
+    if (act && !wn) act[t * n + i] = from_f32<T>(v);
+  }
+  if (act && wn) {                       // the next sublayer's input norm of the row this thread block just wrote
+    row_stats(rr, n, next_kind, eps, red, mean, rstd);
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x)
+      act[t * n + i] = from_f32<T>((rr[i] - mean) * rstd * (offset + to_f32(wn[i])));
   }
 }
 
 template <typename T>
 __global__ void rmsnorm_from_f32_kernel(T* __restrict__ o, const float* __restrict__ r, const int* __restrict__ rows,
-                                        const T* __restrict__ w, int64_t n, float eps, float offset) {
+                                        const T* __restrict__ w, int64_t n, float eps, float offset, int kind) {
   pdl_prologue();
   __shared__ float red[32];
   const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
   const float* x = r + src * n;
-  float ss = 0.f;
-  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(x[i], x[i], ss);
-  ss = block_sum(ss, red);
-  const float rr = 1.0f / sqrtf(ss / (float)n + eps);
+  float mean, rstd;
+  row_stats(x, n, kind, eps, red, mean, rstd);
   for (int64_t i = threadIdx.x; i < n; i += blockDim.x)
-    o[(int64_t)blockIdx.x * n + i] = from_f32<T>(x[i] * rr * (offset + to_f32(w[i])));
+    o[(int64_t)blockIdx.x * n + i] = from_f32<T>((x[i] - mean) * rstd * (offset + to_f32(w[i])));
+}
+
+template <typename T>
+__global__ void gelu_kernel(T* __restrict__ o, const T* __restrict__ x, int64_t total, int tanh_form) {
+  pdl_prologue();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const float v = to_f32(x[i]);
+    const float g = tanh_form ? 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)))
+                              : 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
+    o[i] = from_f32<T>(g);
+  }
+}
+
+template <typename T>
+__global__ void softcap_to_f32_kernel(float* __restrict__ o, const T* __restrict__ x, int64_t total, float cap) {
+  pdl_prologue();
+  const float inv = cap > 0.f ? 1.0f / cap : 0.f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const float v = to_f32(x[i]);
+    o[i] = cap > 0.f ? cap * tanhf(v * inv) : v;
+  }
 }
 
 template <typename T>
@@ -84,43 +129,49 @@ __global__ void relu_squared_kernel(T* __restrict__ o, const T* __restrict__ x, 
 
 extern "C" int b2l_embed_positions(void* residual_f32, void* act, const void* tokens_i32, const void* pos_i32,
                                    const void* embed, const void* pos_table, int64_t rows, int64_t n, int64_t vocab,
-                                   int64_t max_pos, int dtype, void* stream) {
+                                   int64_t max_pos, float scale, int dtype, void* stream) {
   B2L_REQUIRE(residual_f32 && tokens_i32 && pos_i32 && embed, "embed_positions: null pointer");
   B2L_REQUIRE(rows >= 0 && n > 0 && vocab > 0, "embed_positions: bad shape");
   if (rows == 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
   B2L_DISPATCH_FLOAT(dtype, "embed_positions", {
     b2l_launch(embed_positions_kernel<T>, dim3((unsigned)rows), dim3(256), (size_t)0, st, (float*)residual_f32, (T*)act,
-               (const int*)tokens_i32, (const int*)pos_i32, (const T*)embed, (const T*)pos_table, n, vocab, max_pos);
+               (const int*)tokens_i32, (const int*)pos_i32, (const T*)embed, (const T*)pos_table, n, vocab, max_pos, scale);
   });
   B2L_LAUNCH_CHECK();
   return B2L_OK;
 }
 
-extern "C" int b2l_post_norm_residual(void* residual_f32, void* act, const void* y, const void* weight, int64_t rows,
-                                      int64_t n, int64_t y_row_stride, float eps, float weight_offset, int dtype,
-                                      void* stream) {
+extern "C" int b2l_post_norm_residual(void* residual_f32, void* act, const void* y, const void* weight,
+                                      const void* layer_scale, const void* next_weight, int64_t rows, int64_t n,
+                                      int64_t y_row_stride, float eps, float weight_offset, int norm_kind,
+                                      int next_norm_kind, int dtype, void* stream) {
+  B2L_REQUIRE((norm_kind == 0 || norm_kind == 1) && (next_norm_kind == 0 || next_norm_kind == 1),
+              "post_norm_residual: norm kind %d / %d", norm_kind, next_norm_kind);
   B2L_REQUIRE(residual_f32 && y && weight, "post_norm_residual: null pointer");
   B2L_REQUIRE(rows >= 0 && n > 0, "post_norm_residual: bad shape");
   if (rows == 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
   B2L_DISPATCH_FLOAT(dtype, "post_norm_residual", {
     b2l_launch(post_norm_residual_kernel<T>, dim3((unsigned)rows), dim3(256), (size_t)0, st, (float*)residual_f32,
-               (T*)act, (const T*)y, (const T*)weight, n, y_row_stride, eps, weight_offset);
+               (T*)act, (const T*)y, (const T*)weight, (const T*)layer_scale, (const T*)next_weight, n, y_row_stride,
+               eps, weight_offset, norm_kind, next_norm_kind);
   });
   B2L_LAUNCH_CHECK();
   return B2L_OK;
 }
 
 extern "C" int b2l_rmsnorm_from_f32(void* out, const void* residual_f32, const void* rows_i32, const void* weight,
-                                    int64_t rows, int64_t n, float eps, float weight_offset, int dtype, void* stream) {
+                                    int64_t rows, int64_t n, float eps, float weight_offset, int norm_kind, int dtype,
+                                    void* stream) {
   B2L_REQUIRE(out && residual_f32 && weight, "rmsnorm_from_f32: null pointer");
+  B2L_REQUIRE(norm_kind == 0 || norm_kind == 1, "rmsnorm_from_f32: norm kind %d", norm_kind);
   B2L_REQUIRE(rows >= 0 && n > 0, "rmsnorm_from_f32: bad shape");
   if (rows == 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
   B2L_DISPATCH_FLOAT(dtype, "rmsnorm_from_f32", {
     b2l_launch(rmsnorm_from_f32_kernel<T>, dim3((unsigned)rows), dim3(256), (size_t)0, st, (T*)out,
-               (const float*)residual_f32, (const int*)rows_i32, (const T*)weight, n, eps, weight_offset);
+               (const float*)residual_f32, (const int*)rows_i32, (const T*)weight, n, eps, weight_offset, norm_kind);
   });
   B2L_LAUNCH_CHECK();
   return B2L_OK;
@@ -133,6 +184,30 @@ extern "C" int b2l_relu_squared(void* out, const void* x, int64_t total, int dty
   const unsigned grid = (unsigned)(cdiv64(total, 256) < 148 * 16 ? cdiv64(total, 256) : 148 * 16);
   B2L_DISPATCH_FLOAT(dtype, "relu_squared", {
     b2l_launch(relu_squared_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (T*)out, (const T*)x, total);
+  });
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}
+
+extern "C" int b2l_gelu(void* out, const void* x, int64_t total, int tanh_form, int dtype, void* stream) {
+  B2L_REQUIRE(out && x, "gelu: null pointer");
+  if (total <= 0) return B2L_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const unsigned grid = (unsigned)(cdiv64(total, 256) < 148 * 16 ? cdiv64(total, 256) : 148 * 16);
+  B2L_DISPATCH_FLOAT(dtype, "gelu", {
+    b2l_launch(gelu_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (T*)out, (const T*)x, total, tanh_form);
+  });
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}
+
+extern "C" int b2l_softcap_to_f32(void* out_f32, const void* x, int64_t total, float cap, int dtype, void* stream) {
+  B2L_REQUIRE(out_f32 && x, "softcap_to_f32: null pointer");
+  if (total <= 0) return B2L_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const unsigned grid = (unsigned)(cdiv64(total, 256) < 148 * 16 ? cdiv64(total, 256) : 148 * 16);
+  B2L_DISPATCH_FLOAT(dtype, "softcap_to_f32", {
+    b2l_launch(softcap_to_f32_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (float*)out_f32, (const T*)x, total, cap);
   });
   B2L_LAUNCH_CHECK();
   return B2L_OK;

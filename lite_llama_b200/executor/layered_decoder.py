@@ -3,6 +3,12 @@ feed-forward (``FEED_FORWARDS``), around an fp32 residual stream with the norm o
 
     x <- x + norm(mixer(x));   x <- x + norm(ff(x))          (the sublayers read x itself)
 
+or, for designs with ``pre_norm`` (and ``layer_scale``), norms on both sides of each sublayer:
+
+    x <- x + s1 * norm_b(mixer(norm_a(x)));   x <- x + s2 * norm_d(ff(norm_c(x)))
+
+where the output norm, the residual sum and the NEXT sublayer's input norm are one kernel (``post_norm_residual``).
+
 The forward is a flat op list over the library's kernels, like ``executor.decoder.Decoder`` is for the uniform
 rotary decoders (reference: lite_llama/models/base.py:299-319,447-489), but over a RAGGED step (``RaggedBatch``):
 prompt portions and single decode tokens of different requests in one flat ``[tokens, hidden]`` batch.  Projections
@@ -13,6 +19,10 @@ Designs registered here:
   * ``Gufotar``: learned absolute positions, Mamba-2 style state-space layers and position-free attention layers
     (whole-row q/k norm, log-position query gain, tanh soft cap, per-head softmax sink, cross-layer value mixing),
     squared-ReLU feed-forward, zero-centred norm weights.
+  * ``Pesivik``: scaled embedding, layer norms (weight, no bias) before and after every sublayer with a per-channel
+    layer scale, latent attention (low-rank query and key/value latents, a shared rotated key part, sliding window,
+    per-head sigmoid output gate), routed experts (sigmoid router with selection bias and group-limited choice, exact
+    GELU, a shared expert), layers that share another layer's weights, soft-capped logits.
 """
 
 from __future__ import annotations
@@ -26,14 +36,22 @@ from ..kernels import (
     causal_conv_silu,
     embed_positions,
     gated_group_norm,
+    gelu,
+    grouped_experts,
+    head_linear,
+    latent_prepare,
     linear,
     post_norm_residual,
     relu_squared,
     rmsnorm_from_f32,
+    rope_heads,
+    route_sigmoid_groups,
     sink_attention,
+    softcap_to_f32,
     ssm_scan,
 )
-from .model_config import DenseMlpSpec, LayeredConfig, LayerSpec, Mamba2Spec, SinkAttentionSpec
+from .model_config import (DenseMlpSpec, LatentAttentionSpec, LayeredConfig, LayerSpec, Mamba2Spec, MoeMlpSpec,
+                           SinkAttentionSpec)
 from .ragged_batch import RaggedBatch
 from .registry import Architecture, register
 
@@ -41,10 +59,14 @@ from .registry import Architecture, register
 # ------------------------------------------------------------------------------------------------------ weights #
 @dataclass
 class LayeredLayerWeights:
-    norm1: torch.Tensor
+    norm1: torch.Tensor                                  # norm on the mixer's OUTPUT
     mix: dict[str, torch.Tensor]
-    norm2: torch.Tensor | None = None
+    norm2: torch.Tensor | None = None                    # norm on the feed-forward's output
     mlp: dict[str, torch.Tensor] | None = None
+    pre1: torch.Tensor | None = None                     # input norms and layer scales of pre-norm designs
+    pre2: torch.Tensor | None = None
+    ls1: torch.Tensor | None = None
+    ls2: torch.Tensor | None = None
 
 
 @dataclass
@@ -58,7 +80,11 @@ class LayeredWeights:
     def nbytes_per_step(self) -> int:
         """Weight bytes one step streams (embedding / position gathers excluded)."""
         total = self.head.numel() * self.head.element_size()
+        seen = set()
         for lw in self.layers:
+            if id(lw) in seen:                           # a layer that shares another one's weights
+                continue
+            seen.add(id(lw))
             for d in (lw.mix, lw.mlp or {}):
                 total += sum(t.numel() * t.element_size() for t in d.values())
         return total
@@ -119,54 +145,126 @@ def sink_attention_mixer(li: int, spec: SinkAttentionSpec, w: dict[str, torch.Te
         sink_attention(out, qkv, pool, ctx.table, b.seq_start, b.seq_ctx, b.seq_slot, b.portion_list, b.num_portions,
                        b.max_portion, w.get("sink"), *common)
     if b.num_singles:
-        keys = b.max_single_ctx + 1
-        splits = max(1, min(_MAX_SPLITS, -(-keys // _SPLIT_KEYS)))
-        per = -(-keys // splits)
-        per = -(-per // 32) * 32
+        splits, per = split_plan(b.max_single_ctx + 1)
         sink_attention(out, qkv, pool, ctx.table, b.seq_start, b.seq_ctx, b.seq_slot, b.single_list, b.num_singles, 1,
                        w.get("sink"), *common, num_splits=splits, split_keys=per)
     return linear(out, w["o"])
 
 
+def split_plan(keys: int) -> tuple[int, int]:
+    """(ranges, keys per range) of the single-token attention kernel for a token that sees ``keys`` keys."""
+    splits = max(1, min(_MAX_SPLITS, -(-keys // _SPLIT_KEYS)))
+    per = -(-keys // splits)
+    return splits, -(-per // 32) * 32
+
+
+def latent_attention_mixer(li: int, spec: LatentAttentionSpec, w: dict[str, torch.Tensor], x: torch.Tensor,
+                           ctx: StepContext, eps: float) -> torch.Tensor:
+    """One fused down-projection [query latent | key/value latent | shared rotated key part | head gates] -> latent
+    norms, rotation and the cache write (``latent_prepare``) -> query up-projection -> the queries' unrotated parts
+    multiplied into the latent space per head (``W_uk^T q``), their rotated parts turned by the position -> attention
+    over the cached rows [latent | rotated key part] as ONE key/value head whose values are the latent itself (sliding
+    window) -> per-head value up-projection with the sigmoid gate in its epilogue -> output projection.  Equal to
+    expanding per-head keys and values from the latent for every cached token, without doing so."""
+    b = ctx.batch
+    H, dim, rot, rank = spec.heads, spec.head_dim, spec.rot_dim, spec.kv_rank
+    proj = linear(x, w["down"])
+    pool = ctx.kv_buffer[li]
+    latent_prepare(proj, pool, b.kv_rows, b.positions, w["q_norm"], w["kv_norm"], spec.q_rank, rank, rot, spec.rot_dims,
+                   spec.rot_base, eps)
+    q = linear(proj[:, :spec.q_rank], w["uq"])
+    D = rank + rot
+    qa = torch.empty((b.tokens, H * D), dtype=q.dtype, device=q.device)
+    head_linear(qa, D, q, dim + rot, w["uk_t"])
+    if rot:
+        rope_heads(qa[:, rank:], D, q[:, dim:], dim + rot, b.positions, H, rot, spec.rot_dims, spec.rot_base)
+    lat = torch.empty((b.tokens, H * rank), dtype=q.dtype, device=q.device)
+    common = (H, 1, D, rank, spec.scale, 0.0)
+    if b.num_portions:
+        sink_attention(lat, qa, pool, ctx.table, b.seq_start, b.seq_ctx, b.seq_slot, b.portion_list, b.num_portions,
+                       b.max_portion, None, *common, window=spec.window, v_col0=0)
+    if b.num_singles:
+        keys = b.max_single_ctx + 1
+        splits, per = split_plan(min(keys, spec.window) if spec.window else keys)
+        sink_attention(lat, qa, pool, ctx.table, b.seq_start, b.seq_ctx, b.seq_slot, b.single_list, b.num_singles, 1,
+                       None, *common, num_splits=splits, split_keys=per, window=spec.window, v_col0=0)
+    out = torch.empty((b.tokens, H * spec.v_head_dim), dtype=q.dtype, device=q.device)
+    gate = proj[:, spec.q_rank + rank + rot:] if spec.out_gate else None
+    head_linear(out, spec.v_head_dim, lat, rank, w["uv"], gate)
+    return linear(out, w["o"])
+
+
+def _activate(kind: str, x: torch.Tensor) -> torch.Tensor:
+    if kind == "relu2":
+        return relu_squared(x)
+    if kind == "gelu":
+        return gelu(x)
+    if kind == "gelu_tanh":
+        return gelu(x, "tanh")
+    raise ValueError(f"unknown feed-forward activation {kind!r}")
+
+
 def dense_feed_forward(spec: DenseMlpSpec, w: dict[str, torch.Tensor], x: torch.Tensor) -> torch.Tensor:
-    if spec.activation != "relu2":
-        raise ValueError(f"unknown feed-forward activation {spec.activation!r}")
-    return linear(relu_squared(linear(x, w["up"])), w["down"])
+    return linear(_activate(spec.activation, linear(x, w["up"])), w["down"])
 
 
-MIXERS = {"mamba2": mamba2_mixer, "attention": sink_attention_mixer}
-FEED_FORWARDS = {"dense": dense_feed_forward}
+def moe_feed_forward(spec: MoeMlpSpec, w: dict[str, torch.Tensor], x: torch.Tensor) -> torch.Tensor:
+    """Router (product, sigmoid, bias, group-limited top-k: one launch) -> the shared expert as two dense products ->
+    the routed experts as two grouped products; the shared expert's output joins the weighted sum in its kernel."""
+    weights, ids = route_sigmoid_groups(x, w["router"], w.get("correction"), spec.top, spec.groups, spec.keep)
+    shared = None
+    if spec.shared_ff:
+        shared = linear(_activate(spec.activation, linear(x, w["shared_up"])), w["shared_down"])
+    return grouped_experts(x, w["up"], w["down"], weights, ids, addend=shared, activation=spec.activation)
+
+
+MIXERS = {"mamba2": mamba2_mixer, "attention": sink_attention_mixer, "latent_attention": latent_attention_mixer}
+FEED_FORWARDS = {"dense": dense_feed_forward, "moe": moe_feed_forward}
 
 
 class LayeredDecoder:
     def __init__(self, cfg: LayeredConfig, weights: LayeredWeights, device: str = "cuda",
-                 dtype: torch.dtype = torch.bfloat16, norm_weight_offset: float = 1.0) -> None:
+                 dtype: torch.dtype = torch.bfloat16, norm_weight_offset: float | None = None) -> None:
         cfg.validate()
         self.cfg, self.w, self.device, self.dtype = cfg, weights, device, dtype
-        self.norm_offset = norm_weight_offset
+        self.norm_offset = cfg.norm_weight_offset if norm_weight_offset is None else norm_weight_offset
         self.layer_trace: list[torch.Tensor] | None = None       # set to [] to record the residual after every layer
 
     @torch.no_grad()
     def forward(self, tokens: torch.Tensor, batch: RaggedBatch, kv_buffer: dict[int, torch.Tensor],
                 table: torch.Tensor, states, want_rows: torch.Tensor | None = None) -> torch.Tensor:
-        """``tokens [T]`` int32 -> logits ``[T or len(want_rows), vocab]`` in the activation dtype."""
-        cfg, eps, off = self.cfg, self.cfg.rms_norm_eps, self.norm_offset
+        """``tokens [T]`` int32 -> logits ``[T or len(want_rows), vocab]`` in the activation dtype (fp32 when the
+        design soft-caps its logits)."""
+        cfg, eps, off, kind = self.cfg, self.cfg.rms_norm_eps, self.norm_offset, self.cfg.norm_kind
         ctx = StepContext(batch, kv_buffer, table, states)
-        resid, act = embed_positions(tokens, batch.positions, self.w.embed, self.w.pos)
+        pre = cfg.pre_norm
+        resid, act = embed_positions(tokens, batch.positions, self.w.embed, self.w.pos, want_act=not pre,
+                                     scale=cfg.embed_scale)
+        if pre and cfg.layers:
+            act = rmsnorm_from_f32(resid, self.w.layers[0].pre1, eps, off, None, kind)
+        count = len(cfg.layers)
         for li, (spec, lw) in enumerate(zip(cfg.layers, self.w.layers)):
             x = resid if act is None else act
             y = MIXERS[spec.kind](li, spec.mixer, lw.mix, x, ctx, eps)
-            act = post_norm_residual(resid, y, lw.norm1, eps, off)
+            # the norm the NEXT sublayer reads through (pre-norm designs): this layer's feed-forward, else the next layer
+            after = self.w.layers[li + 1].pre1 if li + 1 < count else None
+            nxt = (lw.pre2 if spec.mlp is not None else after) if pre else None
+            act = post_norm_residual(resid, y, lw.norm1, eps, off, kind=kind, layer_scale=lw.ls1, next_weight=nxt,
+                                     next_kind=kind, want_act=not pre or nxt is not None)
             if spec.mlp is not None:
                 x = resid if act is None else act
-                y = FEED_FORWARDS["dense"](spec.mlp, lw.mlp, x)
-                act = post_norm_residual(resid, y, lw.norm2, eps, off)
+                y = FEED_FORWARDS[spec.mlp.kind](spec.mlp, lw.mlp, x)
+                nxt = after if pre else None
+                act = post_norm_residual(resid, y, lw.norm2, eps, off, kind=kind, layer_scale=lw.ls2, next_weight=nxt,
+                                         next_kind=kind, want_act=not pre or nxt is not None)
             if self.layer_trace is not None:
                 self.layer_trace.append(resid.clone())
         if want_rows is not None and want_rows.numel() == 0:
-            return torch.empty((0, cfg.vocab_size), dtype=self.dtype, device=resid.device)
-        hidden = rmsnorm_from_f32(resid, self.w.final_norm, eps, off, want_rows)
-        return linear(hidden, self.w.head)
+            return torch.empty((0, cfg.vocab_size), dtype=torch.float32 if cfg.logit_softcap else self.dtype,
+                               device=resid.device)
+        hidden = rmsnorm_from_f32(resid, self.w.final_norm, eps, off, want_rows, kind)
+        logits = linear(hidden, self.w.head)
+        return softcap_to_f32(logits, cfg.logit_softcap) if cfg.logit_softcap else logits
 
 
 # ---------------------------------------------------------------------------------------------- Gufotar plumbing #
@@ -269,4 +367,134 @@ def random_gufotar_tensors(cfg: LayeredConfig, seed: int = 0) -> dict[str, torch
     return out
 
 
-register(Architecture("Gufotar", parse_gufotar_config, map_gufotar_weights, LayeredDecoder, ragged_steps=True))
+register(Architecture("Gufotar", parse_gufotar_config, map_gufotar_weights, LayeredDecoder, ragged_steps=True,
+                      sources=("gemm_dense", "gemm_simt", "residual_stream", "ssm_scan", "attention_sink", "elementwise")))
+
+
+# ---------------------------------------------------------------------------------------------- Pesivik plumbing #
+def _router_spec(mlp: dict) -> MoeMlpSpec:
+    r = mlp["router"]
+    g = r.get("groups") or {}
+    shared = mlp.get("shared") or {}
+    return MoeMlpSpec(experts=int(r["experts"]), top=int(r["top"]), ff=int(mlp["expert"]["ff"]),
+                      groups=int(g.get("count", 1)), keep=int(g.get("keep", g.get("count", 1))),
+                      shared_ff=int(shared.get("ff", 0)), activation="gelu")
+
+
+def parse_pesivik_config(raw: dict) -> LayeredConfig:
+    layers = []
+    for entry in raw["layers"]:
+        kind, m = entry["type"], entry["mixer"]
+        if kind != "latent_attention":
+            raise ValueError(f"unknown layer type {kind!r}")
+        rot = m.get("rot") or {}
+        rot_dim = int(m.get("rot_dim", 0))
+        mixer = LatentAttentionSpec(heads=int(m["heads"]), head_dim=int(m["dim"]), rot_dim=rot_dim,
+                                    v_head_dim=int(m.get("vdim", m["dim"])), q_rank=int(m["q_rank"]),
+                                    kv_rank=int(m["kv_rank"]), scale=float(m["scale"]),
+                                    rot_dims=int(rot.get("dims", rot_dim)), rot_base=float(rot.get("base", 10000.0)),
+                                    window=int((m.get("mask") or {}).get("size", 0)), out_gate=True)
+        mlp = entry.get("mlp")
+        if mlp is not None and mlp.get("kind", "moe") != "moe":
+            raise ValueError(f"unknown feed-forward kind {mlp.get('kind')!r}")
+        layers.append(LayerSpec(kind, mixer, _router_spec(mlp) if mlp is not None else None,
+                                weights_of=entry.get("weights_of")))
+    return LayeredConfig(name=raw.get("architecture", "Pesivik"), hidden_size=int(raw["width"]),
+                         vocab_size=int(raw["vocab"]), max_seq_len=0, rms_norm_eps=float(raw["norm"]["eps"]),
+                         layers=tuple(layers), norm_kind="layer", pre_norm=True, layer_scale=True,
+                         norm_weight_offset=0.0, learned_positions=False,
+                         embed_scale=float((raw.get("embedding") or {}).get("scale", 1.0)),
+                         logit_softcap=float(raw.get("logit_softcap") or 0.0))
+
+
+def map_pesivik_weights(cfg: LayeredConfig, tensors: dict[str, torch.Tensor], device: str,
+                        dtype: torch.dtype) -> LayeredWeights:
+    """Checkpoint names -> the decoder's weights.  The three projections that read the mixer input (query latent,
+    key/value latent + rotated key part, head gates) are row-concatenated into one GEMM weight, padded with zero rows
+    to a multiple of 8; the key up-projection is stored transposed per head (the queries are multiplied into the latent
+    space); the experts are stacked.  A layer with ``weights_of`` gets the very object of the layer it names."""
+
+    def get(name: str) -> torch.Tensor:
+        if name not in tensors:
+            raise KeyError(f"checkpoint has no tensor {name!r}")
+        return tensors[name].to(device=device, dtype=dtype).contiguous()
+
+    out = LayeredWeights(embed=get("embed"), pos=None, final_norm=get("final.norm"), head=get("head"))
+    built: dict[int, LayeredLayerWeights] = {}
+    for i, spec in enumerate(cfg.layers):
+        if spec.weights_of is not None:
+            continue
+        m, p = spec.mixer, f"l{i}.mix."
+        down = torch.cat([get(p + "dq"), get(p + "dkv"), get(p + "g")], dim=0)
+        pad = -down.shape[0] % 8
+        if pad:
+            down = torch.cat([down, down.new_zeros((pad, down.shape[1]))], dim=0)
+        uk = get(p + "uk").view(m.heads, m.head_dim, m.kv_rank)
+        mix = {"down": down.contiguous(), "q_norm": get(p + "dq.norm"), "kv_norm": get(p + "dkv.norm"),
+               "uq": get(p + "uq"), "uk_t": uk.transpose(1, 2).contiguous(),
+               "uv": get(p + "uv").view(m.heads, m.v_head_dim, m.kv_rank).contiguous(), "o": get(p + "o")}
+        lw = LayeredLayerWeights(norm1=get(f"l{i}.norm1b"), mix=mix, pre1=get(f"l{i}.norm1"), ls1=get(f"l{i}.ls1"))
+        if spec.mlp is not None:
+            q = f"l{i}.mlp."
+            lw.pre2, lw.norm2, lw.ls2 = get(f"l{i}.norm2"), get(f"l{i}.norm2b"), get(f"l{i}.ls2")
+            lw.mlp = {"router": get(q + "router"),
+                      "up": torch.stack([get(f"{q}e{e}.up") for e in range(spec.mlp.experts)]).contiguous(),
+                      "down": torch.stack([get(f"{q}e{e}.down") for e in range(spec.mlp.experts)]).contiguous()}
+            if q + "correction" in tensors:
+                lw.mlp["correction"] = get(q + "correction")
+            if spec.mlp.shared_ff:
+                lw.mlp["shared_up"], lw.mlp["shared_down"] = get(q + "shared.up"), get(q + "shared.down")
+        built[i] = lw
+    out.layers = [built[i if s.weights_of is None else s.weights_of] for i, s in enumerate(cfg.layers)]
+    return out
+
+
+def pesivik_tensor_shapes(cfg: LayeredConfig) -> dict[str, tuple[int, ...]]:
+    """Checkpoint tensor names and shapes of a configuration (random initialisation, shape checks)."""
+    w = cfg.hidden_size
+    shapes: dict[str, tuple[int, ...]] = {"embed": (cfg.vocab_size, w)}
+    for i, spec in enumerate(cfg.layers):
+        if spec.weights_of is not None:
+            continue
+        p, m = f"l{i}.mix.", spec.mixer
+        for n in ("norm1", "norm1b", "ls1"):
+            shapes[f"l{i}.{n}"] = (w,)
+        shapes.update({p + "dq": (m.q_rank, w), p + "dq.norm": (m.q_rank,), p + "uq": (m.heads * (m.head_dim + m.rot_dim), m.q_rank),
+                       p + "dkv": (m.kv_rank + m.rot_dim, w), p + "dkv.norm": (m.kv_rank,),
+                       p + "uk": (m.heads * m.head_dim, m.kv_rank), p + "uv": (m.heads * m.v_head_dim, m.kv_rank),
+                       p + "g": (m.heads, w), p + "o": (w, m.heads * m.v_head_dim)})
+        if spec.mlp is not None:
+            q = f"l{i}.mlp."
+            for n in ("norm2", "norm2b", "ls2"):
+                shapes[f"l{i}.{n}"] = (w,)
+            for e in range(spec.mlp.experts):
+                shapes[f"{q}e{e}.up"], shapes[f"{q}e{e}.down"] = (spec.mlp.ff, w), (w, spec.mlp.ff)
+            shapes[q + "router"], shapes[q + "correction"] = (spec.mlp.experts, w), (spec.mlp.experts,)
+            if spec.mlp.shared_ff:
+                shapes[q + "shared.up"], shapes[q + "shared.down"] = (spec.mlp.shared_ff, w), (w, spec.mlp.shared_ff)
+    shapes.update({"final.norm": (w,), "head": (cfg.vocab_size, w)})
+    return shapes
+
+
+def random_pesivik_tensors(cfg: LayeredConfig, seed: int = 0) -> dict[str, torch.Tensor]:
+    """Seeded random bf16 tensors with checkpoint names (benchmarks and tests; no trained checkpoints exist offline)."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in pesivik_tensor_shapes(cfg).items():
+        leaf = name.rsplit(".", 1)[-1]
+        if len(shape) == 2:
+            t = torch.randn(shape, generator=g) / (shape[1] ** 0.5)
+        elif leaf == "correction":
+            t = 0.1 * torch.randn(shape, generator=g)
+        elif leaf in ("ls1", "ls2"):
+            t = 0.5 + 0.1 * torch.randn(shape, generator=g)
+        else:                                              # norm weights
+            t = 1.0 + 0.1 * torch.randn(shape, generator=g)
+        out[name] = t.to(torch.bfloat16)
+    return out
+
+
+_PESIVIK_SOURCES = ("gemm_dense", "gemm_simt", "residual_stream", "attention_sink", "latent_attention", "moe_routing",
+                    "elementwise")
+register(Architecture("Pesivik", parse_pesivik_config, map_pesivik_weights, LayeredDecoder, ragged_steps=True,
+                      sources=_PESIVIK_SOURCES))

@@ -124,18 +124,76 @@ class SinkAttentionSpec:
         if self.heads % self.kv_heads or self.v_head_dim > 256:
             raise ValueError(f"unsupported attention geometry: {self}")
 
+    @property
+    def cache_row_width(self) -> int:                  # one token's pool row: all K heads, then all V heads
+        return self.kv_heads * (self.head_dim + self.v_head_dim)
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention through low-rank latents: queries ``h -> q_rank -> heads x (head_dim + rot_dim)``; keys / values
+    ``h -> kv_rank`` (the cached latent) ``-> heads x head_dim`` keys and ``heads x v_head_dim`` values, plus one
+    ``rot_dim``-wide rotated key part shared by all heads (cached beside the latent).  Rotary positions act on the
+    first ``rot_dims`` entries of the rotated parts (rotate-half pairing, base ``rot_base``).  ``window`` > 0: a token
+    sees itself and the ``window - 1`` tokens before it.  ``out_gate``: a per-head sigmoid gate on the head outputs."""
+
+    heads: int
+    head_dim: int
+    rot_dim: int
+    v_head_dim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    rot_dims: int
+    rot_base: float = 10000.0
+    window: int = 0
+    out_gate: bool = True
+
+    def validate(self) -> None:
+        if min(self.heads, self.head_dim, self.v_head_dim, self.q_rank, self.kv_rank) < 1 or self.rot_dim < 0 or \
+                self.rot_dims % 2 or not 0 <= self.rot_dims <= self.rot_dim or self.window < 0 or self.kv_rank > 256:
+            raise ValueError(f"unsupported latent attention geometry: {self}")
+
+    @property
+    def cache_row_width(self) -> int:                  # [latent | rotated key part], padded to 16-byte vectors
+        return -(-(self.kv_rank + self.rot_dim) // 8) * 8
+
 
 @dataclass(frozen=True)
 class DenseMlpSpec:
     ff: int
-    activation: str = "relu2"
+    activation: str = "relu2"                          # "relu2" | "gelu" | "gelu_tanh"
+    kind: str = "dense"                                # key of executor.layered_decoder.FEED_FORWARDS
+
+
+@dataclass(frozen=True)
+class MoeMlpSpec:
+    """Routed ungated experts ``W_down act(W_up h)`` + an optional shared one that every token uses.  Sigmoid router
+    scores; the choice adds a per-expert selection bias; ``groups`` runs of neighbouring experts compete with the sum
+    of their two best choice scores and only the ``keep`` best groups are eligible; the ``top`` winners' weights are
+    their scores over the winners' sum."""
+
+    experts: int
+    top: int
+    ff: int
+    groups: int = 1
+    keep: int = 1
+    shared_ff: int = 0
+    activation: str = "gelu"
+    kind: str = "moe"
+
+    def validate(self) -> None:
+        if self.experts < 1 or not 1 <= self.top <= self.experts or self.groups < 1 or self.experts % self.groups or \
+                not 1 <= self.keep <= self.groups or self.keep * (self.experts // self.groups) < self.top:
+            raise ValueError(f"unsupported expert routing: {self}")
 
 
 @dataclass(frozen=True)
 class LayerSpec:
     kind: str                                          # key of executor.layered_decoder.MIXERS
-    mixer: Mamba2Spec | SinkAttentionSpec
-    mlp: DenseMlpSpec | None = None
+    mixer: Mamba2Spec | SinkAttentionSpec | LatentAttentionSpec
+    mlp: DenseMlpSpec | MoeMlpSpec | None = None
+    weights_of: int | None = None                      # the layer whose tensors this one uses (cache / state are its own)
 
 
 @dataclass(frozen=True)
@@ -143,23 +201,39 @@ class LayeredConfig:
     name: str
     hidden_size: int
     vocab_size: int
-    max_seq_len: int                                   # learned position table length
+    max_seq_len: int                                   # learned position table length; 0 = bounded by the KV pool only
     rms_norm_eps: float
     layers: tuple[LayerSpec, ...] = ()
+    norm_kind: str = "rms"                             # "rms" | "layer" (layer norm with a weight, no bias)
+    pre_norm: bool = False                             # sublayers read norm(x) (with norms on their outputs as well)
+    layer_scale: bool = False                          # per-channel scale on each sublayer's normed output
+    norm_weight_offset: float = 1.0                    # 1: norm weights stored around zero; 0: plain weights
+    learned_positions: bool = True
+    embed_scale: float = 1.0
+    logit_softcap: float = 0.0
 
     @property
     def num_layers(self) -> int:
         return len(self.layers)
 
     def attention_layers(self) -> list[int]:
-        return [i for i, l in enumerate(self.layers) if isinstance(l.mixer, SinkAttentionSpec)]
+        """Layers that keep rows in the KV pool (their mixer spec names the row width)."""
+        return [i for i, l in enumerate(self.layers) if hasattr(l.mixer, "cache_row_width")]
 
     def recurrent_layers(self) -> list[int]:
         return [i for i, l in enumerate(self.layers) if isinstance(l.mixer, Mamba2Spec)]
 
     def validate(self) -> None:
-        for l in self.layers:
+        for i, l in enumerate(self.layers):
             l.mixer.validate()
+            if isinstance(l.mlp, MoeMlpSpec):
+                l.mlp.validate()
+            if l.weights_of is not None:
+                j = l.weights_of
+                if not 0 <= j < len(self.layers) or j == i or self.layers[j].weights_of is not None:
+                    raise ValueError(f"layer {i} shares the weights of layer {j}, which has none of its own")
+                if (self.layers[j].kind, self.layers[j].mixer, self.layers[j].mlp) != (l.kind, l.mixer, l.mlp):
+                    raise ValueError(f"layer {i} shares the weights of layer {j} but differs from it")
         shared = {l.mixer.kv_heads * l.mixer.v_head_dim for l in self.layers
                   if isinstance(l.mixer, SinkAttentionSpec) and l.mixer.v_mix}
         if len(shared) > 1:

@@ -289,11 +289,11 @@ class ModelRunner:
 
         self.num_layers = config.num_layers
         self.vocab_size = config.vocab_size
-        self.max_seq_len = config.max_seq_len
+        # a design without a position table takes sequences as long as the pool
+        self.max_seq_len = config.max_seq_len if config.max_seq_len > 0 else max_tokens
         self.max_request_num = max_requests
         attn = config.attention_layers()
-        widths = [config.layers[i].mixer.kv_heads * (config.layers[i].mixer.head_dim + config.layers[i].mixer.v_head_dim)
-                  for i in attn]
+        widths = [config.layers[i].mixer.cache_row_width for i in attn]
         self.kv_cache_manager = KVCacheManager(len(attn), 0, 0, max_tokens, dtype=self.dtype, device=self.device,
                                                row_widths=widths)
         self.kv_buffer_of = dict(zip(attn, self.kv_cache_manager.gpu_kv_buffer))

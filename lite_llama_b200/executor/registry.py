@@ -20,6 +20,7 @@ class Architecture:
     map_weights: Callable[..., Any]                   # (config, {name: tensor}, device, dtype) -> weights object
     model_cls: Any                                    # (config, weights, device=..., dtype=...) -> model
     ragged_steps: bool = True                         # serves prompt portions and decode tokens in one flat batch
+    sources: tuple[str, ...] | None = None            # CUDA sources its forward launches (``build(sources=...)``)
 
 
 _REGISTRY: dict[str, Architecture] = {}
@@ -42,13 +43,18 @@ def names() -> list[str]:
     return sorted(a.name for a in _REGISTRY.values())
 
 
-def read_config(model_dir: str | Path) -> tuple[Architecture, Any]:
-    """``config.json`` of a checkpoint directory -> (architecture entry, parsed config)."""
+def architecture_of(model_dir: str | Path) -> tuple[Architecture, dict]:
+    """The registry entry a checkpoint directory's ``config.json`` names, and the raw configuration."""
     raw = json.loads((Path(model_dir) / "config.json").read_text())
     name = raw.get("architecture") or (raw.get("architectures") or [None])[0] or raw.get("model_type")
     if not name:
         raise ValueError("config.json names no architecture")
-    arch = lookup(name)
+    return lookup(name), raw
+
+
+def read_config(model_dir: str | Path) -> tuple[Architecture, Any]:
+    """``config.json`` of a checkpoint directory -> (architecture entry, parsed config)."""
+    arch, raw = architecture_of(model_dir)
     cfg = arch.parse_config(raw)
     cfg.validate()
     return arch, cfg

@@ -7,9 +7,10 @@ hand-written sm_100a CUDA from ``libb200lite.so`` on the current CUDA stream.
 
 from .flashattention2_nopad import flash_attention2_no_pad
 from .flashdecoding import flash_decoding
-from .fused_moe import fused_moe, moe_align_block_size, route_topk
+from .fused_moe import fused_moe, grouped_experts, moe_align_block_size, route_sigmoid_groups, route_topk
+from .latent import head_linear, latent_prepare, rope_heads
 from .linear import linear, linear_simt
-from .residual_stream import embed_positions, post_norm_residual, relu_squared, rmsnorm_from_f32
+from .residual_stream import embed_positions, gelu, post_norm_residual, relu_squared, rmsnorm_from_f32, softcap_to_f32
 from .sink_attention import attn_prepare, sink_attention
 from .ssm import causal_conv_silu, gated_group_norm, ssm_scan
 from .rope_emb import rope_emb_forward, rope_emb_inplace, rope_kv_write
@@ -26,6 +27,13 @@ __all__ = [
     "fused_moe",
     "moe_align_block_size",
     "route_topk",
+    "route_sigmoid_groups",
+    "grouped_experts",
+    "head_linear",
+    "latent_prepare",
+    "rope_heads",
+    "gelu",
+    "softcap_to_f32",
     "linear",
     "linear_simt",
     "embed_positions",

@@ -6,7 +6,7 @@ from __future__ import annotations
 
 import torch
 
-from ._common import check, dtype_code, index_width, lib, ptr, require_cuda, stream_handle
+from ._common import check, dtype_code, float_code, index_width, lib, ptr, require_cuda, stream_handle
 
 _KIND_F16, _KIND_FP8, _KIND_INT8 = 0, 1, 2
 
@@ -143,8 +143,8 @@ def fused_moe(
               group_k)
 
     out = torch.empty((num_tokens, hidden), device=device, dtype=dtype)
-    check(lib().b2l_moe_sum(out.data_ptr(), expanded.data_ptr(), num_tokens, hidden, top_k, dtype_code(out, "out"),
-                            stream_handle()))
+    check(lib().b2l_moe_sum(out.data_ptr(), expanded.data_ptr(), None, num_tokens, hidden, top_k,
+                            dtype_code(out, "out"), stream_handle()))
     return out
 
 
@@ -165,3 +165,64 @@ def route_topk(router_logits: torch.Tensor, top_k: int, renormalize: bool = True
         )
     )
     return w, ids
+
+
+@torch.no_grad()
+def route_sigmoid_groups(x: torch.Tensor, router_w: torch.Tensor, bias: torch.Tensor | None, top_k: int,
+                         groups: int = 1, keep: int = 1):
+    """Sigmoid router with a selection bias and group-limited choice, the router product included, in one launch:
+    ``s = sigmoid(router_w @ x)`` in fp32; experts compete with ``s + bias``; they form ``groups`` runs of neighbours,
+    a group scores the sum of its two best, only the ``keep`` best groups are eligible; the ``top_k`` winners' weights
+    are their ``s`` over the winners' sum.  Returns ``(weights fp32 [T, k], ids int32 [T, k])``.  The reference's
+    router is a softmax over all experts (lite_llama/models/qwen3_moe.py:94-100, ``route_topk``)."""
+    require_cuda(x, router_w, bias)
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    if router_w.dtype != x.dtype or (bias is not None and bias.dtype != x.dtype):
+        raise ValueError("route_sigmoid_groups: router weight and bias must be in the activation dtype")
+    tokens, k = x.shape
+    e = router_w.shape[0]
+    w = torch.empty((tokens, top_k), dtype=torch.float32, device=x.device)
+    ids = torch.empty((tokens, top_k), dtype=torch.int32, device=x.device)
+    check(lib().b2l_moe_route_sigmoid_groups(w.data_ptr(), ids.data_ptr(), x.data_ptr(), x.stride(0),
+                                             router_w.contiguous().data_ptr(), ptr(bias), tokens, e, k, int(top_k),
+                                             int(groups), int(keep), float_code(x, "x"), stream_handle()))
+    return w, ids
+
+
+@torch.no_grad()
+def grouped_experts(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, weights: torch.Tensor,
+                    ids: torch.Tensor, addend: torch.Tensor | None = None, activation: str = "gelu") -> torch.Tensor:
+    """``sum_k weights[t, k] * W_down[e] act(W_up[e] x[t]) (+ addend[t])`` over each token's chosen experts
+    ``e = ids[t, k]``: ungated two-matrix experts, ``w_up [E, ff, h]``, ``w_down [E, h, ff]``.  Slots are sorted by
+    expert (``moe_align_block_size``), both products run grouped on the CUDA cores with the activation in the first
+    one's epilogue and the fp32 routing weight in the second's; fp16 / bf16 / true fp32.  The gated (SwiGLU) experts of
+    the reference's family are ``fused_moe``."""
+    require_cuda(x, w_up, w_down, weights, ids, addend)
+    if activation != "gelu":
+        raise ValueError(f"grouped_experts: unknown activation {activation!r}")
+    if weights.dtype != torch.float32:
+        raise ValueError("grouped_experts: routing weights are fp32")
+    tokens, hidden = x.shape
+    num_experts, ff, _ = w_up.shape
+    top_k = ids.shape[1]
+    L = lib()
+    block = L.b2l_moe_gemm_simt_block()
+    sorted_ids, expert_ids, num_post = moe_align_block_size(ids, block, num_experts)
+    slots = tokens * top_k
+    code = float_code(x, "x")
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    w_up, w_down = w_up.contiguous(), w_down.contiguous()
+    mid = torch.empty((slots, ff), dtype=x.dtype, device=x.device)
+    check(L.b2l_moe_gemm_simt(mid.data_ptr(), x.data_ptr(), w_up.data_ptr(), None, sorted_ids.data_ptr(),
+                              expert_ids.data_ptr(), num_post.data_ptr(), sorted_ids.numel(), slots, top_k, ff, hidden,
+                              x.stride(0), mid.stride(0), 1, code, stream_handle()))
+    expanded = torch.empty((slots, hidden), dtype=x.dtype, device=x.device)
+    flat_w = weights.reshape(-1).contiguous()
+    check(L.b2l_moe_gemm_simt(expanded.data_ptr(), mid.data_ptr(), w_down.data_ptr(), flat_w.data_ptr(),
+                              sorted_ids.data_ptr(), expert_ids.data_ptr(), num_post.data_ptr(), sorted_ids.numel(),
+                              slots, 1, hidden, ff, mid.stride(0), expanded.stride(0), 0, code, stream_handle()))
+    out = torch.empty((tokens, hidden), dtype=x.dtype, device=x.device)
+    check(L.b2l_moe_sum(out.data_ptr(), expanded.data_ptr(), ptr(addend), tokens, hidden, top_k, code, stream_handle()))
+    return out
