@@ -111,6 +111,23 @@ def route(h: np.ndarray, router_w: np.ndarray, correction: np.ndarray, r: dict) 
     return chosen, weights / (weights.sum() + 1e-20)
 
 
+def route_margin(h: np.ndarray, router_w: np.ndarray, correction: np.ndarray, r: dict) -> float:
+    """How far the choice is from going another way: the smaller of the gap between the last kept and the first dropped
+    group and the gap between the last chosen and the first unchosen eligible expert (inf where there is no rival)."""
+    E, top = r["experts"], r["top"]
+    groups = r.get("groups") or {"count": 1, "keep": 1}
+    choice = sigmoid(router_w @ h) + correction
+    per = E // groups["count"]
+    gscore = [sum(sorted(choice[g * per:(g + 1) * per], reverse=True)[:2]) for g in range(groups["count"])]
+    order = sorted(range(groups["count"]), key=lambda g: (-gscore[g], g))
+    kept = order[:groups["keep"]]
+    gap = gscore[order[groups["keep"] - 1]] - gscore[order[groups["keep"]]] if groups["keep"] < groups["count"] else math.inf
+    eligible = sorted((choice[e] for g in kept for e in range(g * per, (g + 1) * per)), reverse=True)
+    if top < len(eligible):
+        gap = min(gap, eligible[top - 1] - eligible[top])
+    return float(gap)
+
+
 def expert(h: np.ndarray, up: np.ndarray, down: np.ndarray) -> np.ndarray:
     return down @ gelu_erf(up @ h)
 
@@ -137,8 +154,10 @@ def source_layer(config: dict, i: int) -> int:
     return i
 
 
-def forward(config: dict, tensors: dict, tokens: list[int], trace: list | None = None) -> np.ndarray:
-    """Logits ``[T, vocab]`` of one whole sequence; ``trace`` collects the residual stream after every layer."""
+def forward(config: dict, tensors: dict, tokens: list[int], trace: list | None = None,
+            margins: list | None = None) -> np.ndarray:
+    """Logits ``[T, vocab]`` of one whole sequence; ``trace`` collects the residual stream after every layer,
+    ``margins`` one array ``[T]`` of routing margins per routed layer."""
     eps = float(config["norm"]["eps"])
     T = len(tokens)
     pos = list(range(T))
@@ -158,6 +177,9 @@ def forward(config: dict, tensors: dict, tokens: list[int], trace: list | None =
             ls2 = f64(tensors[p + "ls2"])
             mw = _sub(tensors, p + "mlp.")
             y = np.stack([moe(layer_norm(x[t], n2, eps), layer["mlp"], mw) for t in range(T)])
+            if margins is not None:
+                margins.append(np.array([route_margin(layer_norm(x[t], n2, eps), mw["router"], mw["correction"],
+                                                      layer["mlp"]["router"]) for t in range(T)]))
             x = x + np.stack([layer_norm(y[t], n2b, eps) * ls2 for t in range(T)])
         if trace is not None:
             trace.append(x.copy())
@@ -165,3 +187,66 @@ def forward(config: dict, tensors: dict, tokens: list[int], trace: list | None =
     head = f64(tensors["head"])
     logits = np.stack([head @ layer_norm(x[t], fin, eps) for t in range(T)])
     return soft_cap(logits, float(config.get("logit_softcap") or 0.0))
+
+
+# ------------------------------------------------------------------------------------- test models of any size #
+def mixer_entry(heads=3, dim=8, rot_dim=4, vdim=10, q_rank=20, kv_rank=12, window=7, base=10000.0, scale=None) -> dict:
+    return {"dim": dim, "heads": heads, "kv_rank": kv_rank, "mask": {"size": window}, "q_rank": q_rank,
+            "rot": {"base": base, "dims": rot_dim}, "rot_dim": rot_dim,
+            "scale": scale if scale is not None else 1.0 / math.sqrt(dim + rot_dim), "vdim": vdim}
+
+
+def moe_entry(experts=8, top=3, groups=4, keep=2, ff=12, shared_ff=20) -> dict:
+    out = {"expert": {"ff": ff}, "kind": "moe", "router": {"experts": experts, "groups": {"count": groups, "keep": keep},
+                                                            "top": top}}
+    if shared_ff:
+        out["shared"] = {"ff": shared_ff}
+    return out
+
+
+def layer_entry(mixer: dict, mlp: dict | None, weights_of: int | None = None) -> dict:
+    out = {"type": "latent_attention", "mixer": mixer, "mlp": mlp}
+    if weights_of is not None:
+        out["weights_of"] = weights_of
+    return out
+
+
+def make_config(layers: list[dict], width=48, vocab=50, eps=1e-5, embed_scale=0.7, softcap=12.0) -> dict:
+    return {"architecture": "Pesivik", "embedding": {"scale": embed_scale}, "layers": layers, "logit_softcap": softcap,
+            "norm": {"eps": eps}, "vocab": vocab, "width": width}
+
+
+def random_model(config: dict, seed: int = 0, spread: float = 1.0):
+    """Random tensors with checkpoint names, already rounded to bfloat16 values (returned as float32 torch tensors)."""
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    w = config["width"]
+
+    def mat(rows, cols, gain=1.0):
+        return torch.randn(rows, cols, generator=g) * (gain * spread / math.sqrt(cols))
+
+    def vec(n, centre, dev):
+        return centre + dev * torch.randn(n, generator=g)
+
+    t = {"embed": torch.randn(config["vocab"], w, generator=g), "final.norm": vec(w, 1.0, 0.1),
+         "head": mat(config["vocab"], w, 3.0)}
+    for i, layer in enumerate(config["layers"]):
+        if layer.get("weights_of") is not None:
+            continue
+        m, p = layer["mixer"], f"l{i}."
+        H, dim, rot, vdim, qr, kr = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["q_rank"], m["kv_rank"]
+        t.update({p + "norm1": vec(w, 1.0, 0.1), p + "norm1b": vec(w, 1.0, 0.1), p + "ls1": vec(w, 0.5, 0.1),
+                  p + "mix.dq": mat(qr, w), p + "mix.dq.norm": vec(qr, 1.0, 0.1), p + "mix.uq": mat(H * (dim + rot), qr, 2.0),
+                  p + "mix.dkv": mat(kr + rot, w), p + "mix.dkv.norm": vec(kr, 1.0, 0.1),
+                  p + "mix.uk": mat(H * dim, kr, 2.0), p + "mix.uv": mat(H * vdim, kr), p + "mix.g": mat(H, w, 2.0),
+                  p + "mix.o": mat(w, H * vdim)})
+        if layer.get("mlp") is not None:
+            f, r = layer["mlp"], layer["mlp"]["router"]
+            t.update({p + "norm2": vec(w, 1.0, 0.1), p + "norm2b": vec(w, 1.0, 0.1), p + "ls2": vec(w, 0.5, 0.1),
+                      p + "mlp.router": mat(r["experts"], w, 2.0), p + "mlp.correction": vec(r["experts"], -0.3, 0.4)})
+            for e in range(r["experts"]):
+                t[f"{p}mlp.e{e}.up"], t[f"{p}mlp.e{e}.down"] = mat(f["expert"]["ff"], w), mat(w, f["expert"]["ff"])
+            if f.get("shared"):
+                t[p + "mlp.shared.up"], t[p + "mlp.shared.down"] = mat(f["shared"]["ff"], w), mat(w, f["shared"]["ff"])
+    return {k: v.to(torch.bfloat16).float() for k, v in t.items()}
