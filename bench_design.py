@@ -1,4 +1,4 @@
-"""``bench.py --design gufotar``: prefill and decode throughput of the layer-list design at a few sizes that resemble
+"""``bench.py --design gufotar | pesivik``: prefill and decode throughput of a layer-list design at a few sizes that resemble
 a real model's layers (random weights, synthetic ids), beside the closest existing model of the framework (the
 uniform rotary decoder: same width, layer count, attention geometry and feed-forward width), plus every kernel of the
 new path timed alone against its like kernel with the fraction of the measured roofline each reaches.
@@ -254,6 +254,254 @@ def kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) -> list[
     return rows
 
 
+# ------------------------------------------------------------------------------------------------------ Pesivik #
+P_SIZES = {
+    # latent attention: the cached row (kv_rank + rot_dim) is 128 wide, the widest the tensor-core attention tiles take
+    "small": dict(width=1024, layers=4, heads=16, dim=64, rot_dim=32, vdim=64, q_rank=384, kv_rank=96, window=256,
+                  experts=16, top=4, groups=4, keep=2, ff=512, shared_ff=1024, vocab=32000),
+    "1b": dict(width=2048, layers=8, heads=16, dim=128, rot_dim=32, vdim=128, q_rank=768, kv_rank=96, window=256,
+               experts=32, top=4, groups=4, keep=2, ff=1024, shared_ff=2048, vocab=32000),
+    "8b": dict(width=4096, layers=8, heads=32, dim=128, rot_dim=32, vdim=128, q_rank=1536, kv_rank=96, window=256,
+               experts=64, top=8, groups=8, keep=4, ff=1024, shared_ff=2048, vocab=32000),
+}
+
+
+def pesivik_config(sz: dict) -> dict:
+    layer = {"type": "latent_attention",
+             "mixer": {"dim": sz["dim"], "heads": sz["heads"], "kv_rank": sz["kv_rank"], "mask": {"size": sz["window"]},
+                       "q_rank": sz["q_rank"], "rot": {"base": 500000.0, "dims": sz["rot_dim"]}, "rot_dim": sz["rot_dim"],
+                       "scale": 1.0 / math.sqrt(sz["dim"] + sz["rot_dim"]), "vdim": sz["vdim"]},
+             "mlp": {"expert": {"ff": sz["ff"]}, "kind": "moe", "shared": {"ff": sz["shared_ff"]},
+                     "router": {"experts": sz["experts"], "top": sz["top"],
+                                "groups": {"count": sz["groups"], "keep": sz["keep"]}}}}
+    return {"architecture": "Pesivik", "embedding": {"scale": 1.0}, "layers": [dict(layer) for _ in range(sz["layers"])],
+            "logit_softcap": 30.0, "norm": {"eps": 1e-5}, "vocab": sz["vocab"], "width": sz["width"]}
+
+
+def build_pesivik(sz, batch, max_positions, dev, dtype):
+    from lite_llama_b200.executor import ModelRunner
+    from lite_llama_b200.executor.layered_decoder import map_pesivik_weights, parse_pesivik_config, random_pesivik_tensors
+
+    conf = parse_pesivik_config(pesivik_config(sz))
+    conf.validate()
+    weights = map_pesivik_weights(conf, random_pesivik_tensors(conf, seed=0), dev, dtype)
+    return ModelRunner(conf, weights, batch * max_positions, device=dev, dtype=dtype, max_requests=batch)
+
+
+def build_uniform_moe(sz, batch, max_positions, dev):
+    """The closest existing model: the uniform rotary decoder with routed SwiGLU experts (softmax router), same width,
+    depth, head count, expert count, experts per token and expert width; head size = dim + rot_dim, 4 query heads per
+    kv head.  Its expert kernels are fp16-only, so it runs in fp16 (same bytes as bf16)."""
+    from lite_llama_b200.executor import ModelConfig, ModelRunner
+
+    cfg = ModelConfig("uniform-moe-" + str(sz["width"]), sz["width"], sz["layers"], sz["heads"], max(1, sz["heads"] // 4),
+                      128 if sz["dim"] + sz["rot_dim"] > 96 else 64, sz["ff"], sz["vocab"], num_experts=sz["experts"],
+                      num_experts_per_tok=sz["top"], moe_intermediate_size=sz["ff"])
+    return ModelRunner.build(cfg, max_seq_len=max_positions, max_gpu_num_blocks=batch * max_positions, device=dev,
+                             dtype=torch.float16, seed=0)
+
+
+def pesivik_step_throughput(sz, batch, prompt, dev, dtype, flush) -> dict:
+    max_pos = prompt + 64
+    out = {}
+    gen = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, sz["vocab"], (batch, prompt), generator=gen)
+    r = build_pesivik(sz, batch, max_pos, dev, dtype)
+    r.enable_ragged_decode_graphs(widths=(batch,), ctx_buckets=(max_pos,))
+    reqs = []
+
+    def p_prefill():
+        for q in reqs:
+            r.close_request(q)
+        reqs[:] = [r.open_request() for _ in range(batch)]
+        return r.forward_ragged([(q, ids[i].tolist()) for i, q in enumerate(reqs)])
+
+    pre = timed(p_prefill, flush, warmup=2, reps=3)
+    tok = [[int(t)] for t in torch.randint(0, sz["vocab"], (batch,), generator=gen)]
+    state = {"n": 0}
+
+    def p_decode():
+        if state["n"] >= 48:
+            p_prefill()
+            state["n"] = 0
+        state["n"] += 1
+        return r.forward_ragged([(q, tok[i]) for i, q in enumerate(reqs)])
+
+    dec = timed(p_decode, flush, warmup=3, reps=9)
+    out["pesivik"] = {"prefill_ms": pre, "prefill_tok_s": batch * prompt / pre * 1e3, "decode_ms": dec,
+                      "decode_tok_s": batch / dec * 1e3, "weight_bytes_per_step": r.model.w.nbytes_per_step()}
+    del r, reqs
+    gc.collect()
+    torch.cuda.empty_cache()
+    u = build_uniform_moe(sz, batch, max_pos, dev)
+    u.enable_cuda_graph(batch_sizes=(batch,), seq_len_buckets=(max_pos,))
+    lens = torch.full((batch,), prompt, dtype=torch.int64, device=dev)
+    idx = torch.arange(batch, dtype=torch.int64, device=dev)
+    pos = torch.arange(prompt, device=dev).repeat(batch, 1)
+    dids = ids.to(dev)
+
+    def u_prefill():
+        u.kv_cache_manager.free_all()
+        u.prefill_alloc_kv_cache(prompt, lens.clone(), idx)
+        return u.forward(dids, pos, last_token_index=lens - 1)
+
+    pre = timed(u_prefill, flush, warmup=2, reps=3)
+    one = dids[:, :1].contiguous()
+    ustate = {"n": 0}
+
+    def u_decode():
+        if ustate["n"] >= 48:
+            u_prefill()
+            ustate["n"] = 0
+        ustate["n"] += 1
+        u.decode_alloc_kv_cache(batch)
+        return u.forward(one, (u.atten_info.b_seq_len - 1).view(batch, 1))
+
+    dec = timed(u_decode, flush, warmup=3, reps=9)
+    out["uniform_moe_decoder"] = {"prefill_ms": pre, "prefill_tok_s": batch * prompt / pre * 1e3, "decode_ms": dec,
+                                  "decode_tok_s": batch / dec * 1e3, "dtype": "fp16"}
+    del u
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def pesivik_kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) -> list[dict]:
+    """Every kernel of the Pesivik path alone at the size's shapes beside its like kernel of the uniform MoE decoder
+    (fp16 inputs for those), with the fraction of the measured roofline each reaches."""
+    import lite_llama_b200.kernels as K
+
+    es = 2
+    W, H, dim, rot, vdim, qr, kr = sz["width"], sz["heads"], sz["dim"], sz["rot_dim"], sz["vdim"], sz["q_rank"], sz["kv_rank"]
+    E, top, ff, sff, win = sz["experts"], sz["top"], sz["ff"], sz["shared_ff"], sz["window"]
+    D = kr + rot
+    T, ctx = batch * prompt, prompt
+    G = max(1, H // 4)
+    UD = 128 if dim + rot > 96 else 64
+    rows: list[dict] = []
+
+    def i32(v):
+        return torch.tensor(list(v), dtype=torch.int32, device=dev)
+
+    def rnd(*shape, dt=dtype, s=1.0):
+        return (torch.randn(*shape, device=dev) * s).to(dt)
+
+    def add(name, like, fn, nbytes=0, flops=0, like_fn=None, like_bytes=None, like_flops=None):
+        ms = timed(fn, flush)
+        row = {"kernel": name, "us": ms * 1e3}
+        if flops:
+            row.update(tflops=flops / ms / 1e9, frac=flops / ms / 1e9 / tflops, bound="tensor")
+        else:
+            row.update(gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / hbm_gbs, bound="hbm")
+        if like_fn is not None:
+            lms = timed(like_fn, flush)
+            lf = like_flops if like_flops is not None else flops
+            lb = like_bytes if like_bytes is not None else nbytes
+            lfrac = lf / lms / 1e9 / tflops if flops else lb / lms / 1e6 / hbm_gbs
+            row.update(like=like, like_us=lms * 1e3, like_frac=lfrac,
+                       distance_ratio=(lfrac / row["frac"]) if row["frac"] else None)
+        rows.append(row)
+
+    f16 = torch.float16
+    p_start, p_ctx, p_slot = i32(range(0, T + 1, prompt)), i32([0] * batch), i32(range(batch))
+    d_start, d_ctx = i32(range(batch + 1)), i32([ctx] * batch)
+    # ---------------- residual stream: output norm + layer scale + residual + the next input norm in one launch
+    resid = torch.randn(T, W, device=dev)
+    y, wn, ls, wnext = rnd(T, W), rnd(W, s=0.1) + 1, rnd(W, s=0.1) + 0.5, rnd(W, s=0.1) + 1
+    xh, res16, wn16 = rnd(T, W, dt=f16), rnd(T, W, dt=f16), rnd(W, dt=f16, s=0.1)
+    add("post_norm_residual (layer norm, scale, next norm)", "skip_rmsnorm",
+        lambda: K.post_norm_residual(resid, y, wn, 1e-5, 0.0, kind="layer", layer_scale=ls, next_weight=wnext, next_kind="layer"),
+        nbytes=T * W * (4 + 4 + es + es), like_fn=lambda: K.skip_rmsnorm(xh, res16, wn16, 1e-5), like_bytes=T * W * 4 * es)
+    mid = rnd(T, sff)
+    gu = rnd(T, 2 * sff, dt=f16)
+    add("gelu", "swiglu_forward", lambda: K.gelu(mid), nbytes=T * sff * 2 * es,
+        like_fn=lambda: K.swiglu_forward(gu[:, :sff], gu[:, sff:]), like_bytes=T * sff * 3 * es)
+    # ---------------- latent preparation beside the rotary cache write
+    cols = -(-(qr + kr + rot + H) // 8) * 8
+    proj = rnd(T, cols, s=0.5)
+    pool = rnd(batch * (ctx + 1), D, s=0.5)
+    table = torch.arange(batch * (ctx + 1), dtype=torch.int32, device=dev).view(batch, ctx + 1)
+    rows_p = table[:, :ctx].reshape(-1).contiguous()
+    pos_p = i32(list(range(prompt)) * batch)
+    wq, wkv = rnd(qr, s=0.1) + 1, rnd(kr, s=0.1) + 1
+    upool = rnd(batch * (ctx + 1), 2 * G * UD, dt=f16, s=0.5)
+    uqkv = rnd(T, (H + 2 * G) * UD, dt=f16, s=0.5)
+    cos = rnd(batch, prompt, UD, dt=f16)
+    add("latent_prepare", "rope_kv_write",
+        lambda: K.latent_prepare(proj, pool, rows_p, pos_p, wq, wkv, qr, kr, rot, rot, 500000.0, 1e-5),
+        nbytes=T * ((2 * qr + kr + rot) * es + D * es),
+        like_fn=lambda: K.rope_kv_write(uqkv[:, :H * UD].view(T, H, UD), uqkv[:, H * UD:(H + G) * UD].view(T, G, UD),
+                                        uqkv[:, (H + G) * UD:].view(T, G, UD), cos, cos, rows_p, upool.view(-1, 2 * G, UD), batch, prompt),
+        like_bytes=T * ((2 * H + 2 * G) * UD * es + 2 * G * UD * es))
+    # ---------------- per-head products beside the dense GEMM at equal FLOPs
+    q = rnd(T, H * (dim + rot), s=0.5)
+    qa = torch.empty(T, H * D, dtype=dtype, device=dev)
+    ukt = rnd(H, kr, dim, s=0.1)
+    dense_x, dense_w = rnd(T, dim), rnd(H * kr, dim, s=0.1)
+    add("head_linear (queries into the latent space)", "linear (one GEMM of equal FLOPs)",
+        lambda: K.head_linear(qa, D, q, dim + rot, ukt), flops=2 * T * H * kr * dim,
+        like_fn=lambda: K.linear(dense_x, dense_w))
+    add("rope_heads (queries' rotated parts)", None,
+        lambda: K.rope_heads(qa[:, kr:], D, q[:, dim:], dim + rot, pos_p, H, rot, rot, 500000.0), nbytes=T * H * rot * 2 * es)
+    lat = rnd(T, H * kr, s=0.5)
+    o = torch.empty(T, H * vdim, dtype=dtype, device=dev)
+    uv = rnd(H, vdim, kr, s=0.1)
+    dense_x2, dense_w2 = rnd(T, kr), rnd(H * vdim, kr, s=0.1)
+    add("head_linear (values out of the latent, gated)", "linear (one GEMM of equal FLOPs)",
+        lambda: K.head_linear(o, vdim, lat, kr, uv, proj[:, qr + kr + rot:]), flops=2 * T * H * vdim * kr,
+        like_fn=lambda: K.linear(dense_x2, dense_w2))
+    # ---------------- attention over the latent rows (one kv head of width D, values = its first kr columns)
+    scale = 1.0 / math.sqrt(dim + rot)
+    qa = rnd(T, H * D, s=0.5)
+    seen = sum(min(t + 1, win) for t in range(prompt))
+    att_flops = 2 * batch * H * (D + kr) * seen
+    q3, k3, v3 = (uqkv[:, :H * UD].view(T, H, UD), uqkv[:, H * UD:(H + G) * UD].view(T, G, UD),
+                  uqkv[:, (H + G) * UD:].view(T, G, UD))
+    lens = torch.full((batch,), prompt, dtype=torch.int32, device=dev)
+    add("attention over latent rows (prompts, window %d)" % win, "flash_attention2_no_pad (full causal)",
+        lambda: K.sink_attention(lat, qa, pool, table, p_start, p_ctx, p_slot, None, batch, prompt, None, H, 1, D, kr, scale,
+                                 0.0, window=win, v_col0=0),
+        flops=att_flops,
+        like_fn=lambda: K.flash_attention2_no_pad(q3, k3, v3, scale * 1.4426950408889634, p_start[:batch], lens, prompt),
+        like_flops=4 * batch * H * UD * prompt * (prompt + 1) / 2)
+    keys = min(ctx + 1, win)
+    splits = max(1, min(128, -(-keys // 128)))
+    per = -(-(-(-keys // splits)) // 32) * 32
+    seq1 = torch.full((batch,), ctx + 1, dtype=torch.int32, device=dev)
+    uout = torch.empty(T, H * UD, dtype=f16, device=dev)
+    add("attention over latent rows (decode, window %d)" % win, "flash_decoding (context %d)" % (ctx + 1),
+        lambda: K.sink_attention(lat, qa, pool, table, d_start, d_ctx, p_slot, None, batch, 1, None, H, 1, D, kr, scale, 0.0,
+                                 num_splits=splits, split_keys=per, window=win, v_col0=0),
+        nbytes=batch * keys * D * es,
+        like_fn=lambda: K.flash_decoding(q3[:batch], upool.view(-1, 2 * G, UD)[:, :G], upool.view(-1, 2 * G, UD)[:, G:], scale,
+                                         table, p_slot, seq1, ctx + 1),
+        like_bytes=batch * (ctx + 1) * 2 * G * UD * es)
+    # ---------------- router and experts
+    x = rnd(T, W, s=0.5)
+    rw, rb = rnd(E, W, s=0.05), rnd(E, s=0.1)
+    x16, rw16 = x.to(f16), rw.to(f16)
+    add("route_sigmoid_groups (product + choice)", "linear + route_topk",
+        lambda: K.route_sigmoid_groups(x, rw, rb, top, sz["groups"], sz["keep"]), nbytes=T * W * es + E * W * es,
+        like_fn=lambda: K.route_topk(K.linear(x16, rw16), top))
+    wts, ids = K.route_sigmoid_groups(x, rw, rb, top, sz["groups"], sz["keep"])
+    up, down = rnd(E, ff, W, s=0.03), rnd(E, W, ff, s=0.03)
+    w1, w2 = rnd(E, 2 * ff, W, dt=f16, s=0.03), rnd(E, W, ff, dt=f16, s=0.03)
+    tw, tid = K.route_topk(K.linear(x16, rw16), top)
+    add("grouped_experts (prompts)", "fused_moe", lambda: K.grouped_experts(x, up, down, wts, ids),
+        flops=2 * T * top * 2 * ff * W, like_fn=lambda: K.fused_moe(x16, w1, w2, tw, tid),
+        like_flops=2 * T * top * 3 * ff * W)
+    xd, xd16 = x[:batch].contiguous(), x16[:batch].contiguous()
+    wd, idd, twd, tidd = wts[:batch].contiguous(), ids[:batch].contiguous(), tw[:batch].contiguous(), tid[:batch].contiguous()
+    active = len(set(idd.flatten().tolist()))
+    active_u = len(set(tidd.flatten().tolist()))
+    add("grouped_experts (decode)", "fused_moe", lambda: K.grouped_experts(xd, up, down, wd, idd),
+        nbytes=active * 2 * ff * W * es, like_fn=lambda: K.fused_moe(xd16, w1, w2, twd, tidd),
+        like_bytes=active_u * 3 * ff * W * es)
+    logits = rnd(batch, sz["vocab"], s=8.0)
+    add("softcap_to_f32 (logits)", None, lambda: K.softcap_to_f32(logits, 30.0), nbytes=batch * sz["vocab"] * (es + 4))
+    return rows
+
+
 def run(args) -> None:
     from bench import ClockSampler, peaks
 
@@ -263,16 +511,18 @@ def run(args) -> None:
     hbm_gbs, tflops, src = peaks()
     flush = _flush_buffer(dev)
     sizes = [s for s in (args.design_sizes or "small,1b,8b").split(",") if s]
+    table, steps, kernels = ((P_SIZES, pesivik_step_throughput, pesivik_kernel_table) if args.design == "pesivik"
+                             else (SIZES, step_throughput, kernel_table))
     result = {"design": args.design, "dtype": "bf16", "data": "synthetic ids, random weights", "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": tflops, "source": src},
               "batch": args.batch, "prompt_len": args.prompt_len, "l2_policy": "256 MiB written between timed runs", "sizes": {}}
     t0 = time.time()
     with ClockSampler(0) as clocks:
         for name in sizes:
-            sz = SIZES[name]
+            sz = table[name]
             entry = {"geometry": sz}
-            entry["steps"] = step_throughput(sz, args.batch, args.prompt_len, dev, dtype, flush)
+            entry["steps"] = steps(sz, args.batch, args.prompt_len, dev, dtype, flush)
             torch.cuda.empty_cache()
-            entry["kernels"] = kernel_table(sz, args.batch, args.prompt_len, dev, dtype, flush, hbm_gbs, tflops)
+            entry["kernels"] = kernels(sz, args.batch, args.prompt_len, dev, dtype, flush, hbm_gbs, tflops)
             torch.cuda.empty_cache()
             result["sizes"][name] = entry
     result["clocks"] = clocks.summary()

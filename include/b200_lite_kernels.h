@@ -296,6 +296,18 @@ int b2l_moe_gemm_simt(void* c, const void* a, const void* w, const void* slot_we
                       const void* sorted_token_ids, const void* expert_ids, const void* num_tokens_post_padded,
                       int64_t em, int64_t num_valid_slots, int top_k, int64_t n, int64_t k, int64_t a_row_stride,
                       int64_t c_row_stride, int act, int dtype, void* stream);
+/* Tensor-core (mma.sync, fp32 accumulators) versions of b2l_head_linear and b2l_moe_gemm_simt for 16-bit dtypes
+ * (csrc/gemm_rows_mma.cu); b2l_rows_gemm_mma_ok says whether they take the operands (k and the x strides multiples
+ * of 8 elements, 16-byte aligned bases).  b2l_moe_gemm_mma: block_size 16 or 64 = the block size of the alignment. */
+int b2l_rows_gemm_mma_ok(const void* x, const void* w, int64_t k, int64_t x_row_stride, int64_t x_head_stride,
+                         int dtype);
+int b2l_head_linear_mma(void* y, int64_t y_row_stride, int64_t y_head_stride, const void* x, int64_t x_row_stride,
+                        int64_t x_head_stride, const void* w, const void* gate, int64_t gate_row_stride, int64_t m,
+                        int heads, int64_t n, int64_t k, int dtype, void* stream);
+int b2l_moe_gemm_mma(void* c, const void* a, const void* w, const void* slot_weight_f32, const void* sorted_token_ids,
+                     const void* expert_ids, const void* num_tokens_post_padded, int64_t em, int64_t num_valid_slots,
+                     int top_k, int block_size, int64_t n, int64_t k, int64_t a_row_stride, int64_t c_row_stride,
+                     int act, int dtype, void* stream);
 /* Router product + sigmoid scores + selection bias + group-limited top-k in one launch (csrc/moe_routing.cu):
  * z = router_w . x in fp32, s = sigmoid(z), choice = s + bias (nullable); `groups` equal runs of neighbouring experts,
  * group score = sum of its two largest choice scores, only the `keep` best groups are eligible; the top_k largest

@@ -68,8 +68,8 @@ BASE_SOURCES = ("core", "tma_desc")
 # what the layer-list decoders launch between them: dense tcgen05 GEMM, fp32 / odd-shape / per-head / grouped GEMM,
 # residual stream, state-space, attention and latent-attention kernels, expert routing, argmax and expert sum.  Each
 # registered architecture names its own subset (executor.registry.Architecture.sources).
-LAYERED_SOURCES = ("gemm_dense", "gemm_simt", "residual_stream", "ssm_scan", "attention_sink", "latent_attention",
-                   "moe_routing", "elementwise")
+LAYERED_SOURCES = ("gemm_dense", "gemm_simt", "gemm_rows_mma", "residual_stream", "ssm_scan", "attention_sink",
+                   "latent_attention", "moe_routing", "elementwise")
 LINK_STAMP = OBJ_DIR / "link.stamp"
 
 

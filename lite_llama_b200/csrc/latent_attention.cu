@@ -16,17 +16,6 @@
 
 namespace {
 
-__device__ __forceinline__ float block_sum_l(float v, float* red) {
-  v = warp_reduce_sum(v);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  float t = (lane < nw) ? red[lane] : 0.f;
-  t = warp_reduce_sum(t);
-  __syncthreads();
-  return t;
-}
-
 // cos / sin of pos * base^(-2i/dims) for pair i
 __device__ __forceinline__ void pair_angle(int pos, int i, int dims, double log2_base, float& c, float& s) {
   const double f = exp2(-2.0 * (double)i / (double)dims * log2_base);
@@ -35,52 +24,59 @@ __device__ __forceinline__ void pair_angle(int pos, int i, int dims, double log2
   c = (float)cd; s = (float)sd;
 }
 
+// One WARP per token (four tokens per CTA): the two statistics are warp reductions, nothing waits on a barrier.
 template <typename T>
 __global__ void __launch_bounds__(128) latent_prepare_kernel(T* __restrict__ proj, int64_t stride, T* __restrict__ pool,
                                                              int64_t pool_stride, const int* __restrict__ rows,
                                                              const int* __restrict__ pos, const T* __restrict__ wq,
-                                                             const T* __restrict__ wkv, int q_rank, int kv_rank,
-                                                             int rot_dim, int rot_dims, double log2_base, float eps) {
+                                                             const T* __restrict__ wkv, int64_t tokens, int q_rank,
+                                                             int kv_rank, int rot_dim, int rot_dims, double log2_base,
+                                                             float eps) {
   pdl_prologue();
-  __shared__ float red[32];
-  const int64_t t = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int64_t t = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (t >= tokens) return;
   T* a = proj + t * stride;
   const T* b = a + q_rank;
   const T* r = b + kv_rank;
   T* dst = pool + (int64_t)rows[t] * pool_stride;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < q_rank; i += blockDim.x) { const float v = to_f32(a[i]); ss = fmaf(v, v, ss); }
-  float rstd = 1.0f / sqrtf(block_sum_l(ss, red) / (float)q_rank + eps);
-  for (int i = threadIdx.x; i < q_rank; i += blockDim.x) a[i] = from_f32<T>(to_f32(a[i]) * rstd * to_f32(wq[i]));
+  for (int i = lane; i < q_rank; i += 32) { const float v = to_f32(a[i]); ss = fmaf(v, v, ss); }
+  float rstd = 1.0f / sqrtf(warp_reduce_sum(ss) / (float)q_rank + eps);
+  for (int i = lane; i < q_rank; i += 32) a[i] = from_f32<T>(to_f32(a[i]) * rstd * to_f32(wq[i]));
   ss = 0.f;
-  for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) { const float v = to_f32(b[i]); ss = fmaf(v, v, ss); }
-  rstd = 1.0f / sqrtf(block_sum_l(ss, red) / (float)kv_rank + eps);
-  for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) dst[i] = from_f32<T>(to_f32(b[i]) * rstd * to_f32(wkv[i]));
+  for (int i = lane; i < kv_rank; i += 32) { const float v = to_f32(b[i]); ss = fmaf(v, v, ss); }
+  rstd = 1.0f / sqrtf(warp_reduce_sum(ss) / (float)kv_rank + eps);
+  for (int i = lane; i < kv_rank; i += 32) dst[i] = from_f32<T>(to_f32(b[i]) * rstd * to_f32(wkv[i]));
   const int half = rot_dims / 2, p = pos[t];
-  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+  for (int i = lane; i < half; i += 32) {
     float c, s;
     pair_angle(p, i, rot_dims, log2_base, c, s);
     const float u = to_f32(r[i]), v = to_f32(r[i + half]);
     dst[kv_rank + i] = from_f32<T>(u * c - v * s);
     dst[kv_rank + i + half] = from_f32<T>(v * c + u * s);
   }
-  for (int i = 2 * half + threadIdx.x; i < rot_dim; i += blockDim.x) dst[kv_rank + i] = r[i];
+  for (int i = 2 * half + lane; i < rot_dim; i += 32) dst[kv_rank + i] = r[i];
 }
 
 template <typename T>
 __global__ void __launch_bounds__(128) rope_heads_kernel(T* __restrict__ dst, int64_t dst_stride, int dst_head_stride,
                                                          const T* __restrict__ src, int64_t src_stride,
-                                                         int src_head_stride, const int* __restrict__ pos, int heads,
-                                                         int width, int rot_dims, double log2_base) {
+                                                         int src_head_stride, const int* __restrict__ pos,
+                                                         int64_t tokens, int heads, int width, int rot_dims,
+                                                         double log2_base) {
   pdl_prologue();
-  extern __shared__ float cs[];                      // [half] cos, [half] sin of this token
-  const int64_t t = blockIdx.x;
+  extern __shared__ float cs_all[];                  // per warp: [half] cos, [half] sin of its token
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t t = (int64_t)blockIdx.x * 4 + warp;
+  if (t >= tokens) return;
   const int half = rot_dims / 2, p = pos[t];
-  for (int i = threadIdx.x; i < half; i += blockDim.x) pair_angle(p, i, rot_dims, log2_base, cs[i], cs[half + i]);
-  __syncthreads();
+  float* cs = cs_all + warp * 2 * (half > 0 ? half : 1);
+  for (int i = lane; i < half; i += 32) pair_angle(p, i, rot_dims, log2_base, cs[i], cs[half + i]);
+  __syncwarp();
   const T* s = src + t * src_stride;
   T* d = dst + t * dst_stride;
-  for (int i = threadIdx.x; i < heads * width; i += blockDim.x) {
+  for (int i = lane; i < heads * width; i += 32) {
     const int h = i / width, c = i - h * width;
     const T* sh = s + (int64_t)h * src_head_stride;
     float v;
@@ -105,9 +101,9 @@ extern "C" int b2l_latent_prepare(void* proj, int64_t proj_row_stride, void* poo
   cudaStream_t st = (cudaStream_t)stream;
   const double l2b = log2((double)rot_base);
   B2L_DISPATCH_FLOAT(dtype, "latent_prepare", {
-    b2l_launch(latent_prepare_kernel<T>, dim3((unsigned)tokens), dim3(128), (size_t)0, st, (T*)proj, proj_row_stride,
-               (T*)pool, pool_row_stride, (const int*)kv_rows_i32, (const int*)pos_i32, (const T*)q_norm_weight,
-               (const T*)kv_norm_weight, q_rank, kv_rank, rot_dim, rot_dims, l2b, eps);
+    b2l_launch(latent_prepare_kernel<T>, dim3((unsigned)cdiv64(tokens, 4)), dim3(128), (size_t)0, st, (T*)proj,
+               proj_row_stride, (T*)pool, pool_row_stride, (const int*)kv_rows_i32, (const int*)pos_i32,
+               (const T*)q_norm_weight, (const T*)kv_norm_weight, tokens, q_rank, kv_rank, rot_dim, rot_dims, l2b, eps);
   });
   B2L_LAUNCH_CHECK();
   return B2L_OK;
@@ -122,10 +118,10 @@ extern "C" int b2l_rope_heads(void* dst, int64_t dst_row_stride, int dst_head_st
   if (tokens <= 0 || width == 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const double l2b = log2((double)rot_base);
-  const size_t smem = (size_t)(rot_dims > 0 ? rot_dims : 1) * sizeof(float);
+  const size_t smem = (size_t)4 * (rot_dims > 0 ? rot_dims : 2) * sizeof(float);
   B2L_DISPATCH_FLOAT(dtype, "rope_heads", {
-    b2l_launch(rope_heads_kernel<T>, dim3((unsigned)tokens), dim3(128), smem, st, (T*)dst, dst_row_stride,
-               dst_head_stride, (const T*)src, src_row_stride, src_head_stride, (const int*)pos_i32, heads, width,
+    b2l_launch(rope_heads_kernel<T>, dim3((unsigned)cdiv64(tokens, 4)), dim3(128), smem, st, (T*)dst, dst_row_stride,
+               dst_head_stride, (const T*)src, src_row_stride, src_head_stride, (const int*)pos_i32, tokens, heads, width,
                rot_dims, l2b);
   });
   B2L_LAUNCH_CHECK();

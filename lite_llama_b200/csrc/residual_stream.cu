@@ -82,6 +82,104 @@ __global__ void post_norm_residual_kernel(float* __restrict__ r, T* __restrict__
   }
 }
 
+// Register-resident version for rows of up to NV * 1024 elements (n a multiple of 4, 16-byte aligned rows): every
+// thread keeps its float4 slices of y and of the residual row in registers, so each is read once, and the four
+// statistics (mean and deviation sums of y, then of the updated row) are block reductions over registers.  Same
+// arithmetic as the kernel above.
+template <int N> struct RawVec;
+template <> struct RawVec<4> { using type = uint2; };       // four 16-bit elements
+template <> struct RawVec<8> { using type = uint2; };
+template <> struct RawVec<16> { using type = uint4; };      // four 32-bit elements
+
+template <typename T>
+__device__ __forceinline__ void load4(const T* p, float (&v)[4]) {
+  using R = typename RawVec<4 * sizeof(T)>::type;
+  const R raw = *reinterpret_cast<const R*>(p);
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) v[c] = to_f32(e[c]);
+}
+template <typename T>
+__device__ __forceinline__ void store4(T* p, const float (&v)[4]) {
+  using R = typename RawVec<4 * sizeof(T)>::type;
+  R raw;
+  T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) e[c] = from_f32<T>(v[c]);
+  *reinterpret_cast<R*>(p) = raw;
+}
+
+template <int NV>
+__device__ __forceinline__ void reg_stats(const float (&v)[NV][4], int64_t n, int kind, float eps, float* red,
+                                          float& mean, float& rstd) {
+  mean = 0.f;
+  if (kind == 1) {
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+      if ((int64_t)(j * 256 + threadIdx.x) * 4 < n) s += (v[j][0] + v[j][1]) + (v[j][2] + v[j][3]);
+    mean = block_sum(s, red) / (float)n;
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < NV; ++j)
+    if ((int64_t)(j * 256 + threadIdx.x) * 4 < n) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) { const float d = v[j][c] - mean; ss = fmaf(d, d, ss); }
+    }
+  rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)n + eps);
+}
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(256) post_norm_residual_reg_kernel(float* __restrict__ r, T* __restrict__ act,
+                                                                     const T* __restrict__ y, const T* __restrict__ w,
+                                                                     const T* __restrict__ ls, const T* __restrict__ wn,
+                                                                     int64_t n, int64_t ys, float eps, float offset,
+                                                                     int kind, int next_kind) {
+  pdl_prologue();
+  __shared__ float red[32];
+  const int64_t t = blockIdx.x;
+  const T* yr = y + t * ys;
+  float* rr = r + t * n;
+  float yv[NV][4], rv[NV][4];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int64_t i = (int64_t)(j * 256 + threadIdx.x) * 4;
+    if (i < n) { load4(yr + i, yv[j]); load4(rr + i, rv[j]); }
+  }
+  float mean, rstd;
+  reg_stats<NV>(yv, n, kind, eps, red, mean, rstd);
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int64_t i = (int64_t)(j * 256 + threadIdx.x) * 4;
+    if (i >= n) continue;
+    float wv[4], lv[4] = {1.f, 1.f, 1.f, 1.f};
+    load4(w + i, wv);
+    if (ls) load4(ls + i, lv);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      float d = (yv[j][c] - mean) * rstd * (offset + wv[c]);
+      if (ls) d *= lv[c];
+      rv[j][c] += d;
+    }
+    store4(rr + i, rv[j]);
+    if (act && !wn) store4(act + t * n + i, rv[j]);
+  }
+  if (act && wn) {
+    reg_stats<NV>(rv, n, next_kind, eps, red, mean, rstd);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int64_t i = (int64_t)(j * 256 + threadIdx.x) * 4;
+      if (i >= n) continue;
+      float wv[4], o[4];
+      load4(wn + i, wv);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) o[c] = (rv[j][c] - mean) * rstd * (offset + wv[c]);
+      store4(act + t * n + i, o);
+    }
+  }
+}
+
 template <typename T>
 __global__ void rmsnorm_from_f32_kernel(T* __restrict__ o, const float* __restrict__ r, const int* __restrict__ rows,
                                         const T* __restrict__ w, int64_t n, float eps, float offset, int kind) {
@@ -125,6 +223,26 @@ __global__ void relu_squared_kernel(T* __restrict__ o, const T* __restrict__ x, 
   }
 }
 
+template <typename T>
+void launch_post_norm(float* r, T* act, const T* y, const T* w, const T* ls, const T* wn, int64_t rows, int64_t n,
+                      int64_t ys, float eps, float offset, int kind, int next_kind, cudaStream_t st) {
+  constexpr uintptr_t A = 4 * sizeof(T);
+  auto al = [](const void* p, uintptr_t a) { return p == nullptr || (uintptr_t)p % a == 0; };
+  const bool fast = n % 4 == 0 && n <= 8 * 1024 && ys % 4 == 0 && al(r, 16) && al(act, A) && al(y, A) && al(w, A) &&
+                    al(ls, A) && al(wn, A);
+  const dim3 grid((unsigned)rows), block(256);
+  if (fast && n <= 1024)
+    b2l_launch(post_norm_residual_reg_kernel<T, 1>, grid, block, (size_t)0, st, r, act, y, w, ls, wn, n, ys, eps, offset, kind, next_kind);
+  else if (fast && n <= 2048)
+    b2l_launch(post_norm_residual_reg_kernel<T, 2>, grid, block, (size_t)0, st, r, act, y, w, ls, wn, n, ys, eps, offset, kind, next_kind);
+  else if (fast && n <= 4096)
+    b2l_launch(post_norm_residual_reg_kernel<T, 4>, grid, block, (size_t)0, st, r, act, y, w, ls, wn, n, ys, eps, offset, kind, next_kind);
+  else if (fast)
+    b2l_launch(post_norm_residual_reg_kernel<T, 8>, grid, block, (size_t)0, st, r, act, y, w, ls, wn, n, ys, eps, offset, kind, next_kind);
+  else
+    b2l_launch(post_norm_residual_kernel<T>, grid, block, (size_t)0, st, r, act, y, w, ls, wn, n, ys, eps, offset, kind, next_kind);
+}
+
 }  // namespace
 
 extern "C" int b2l_embed_positions(void* residual_f32, void* act, const void* tokens_i32, const void* pos_i32,
@@ -153,9 +271,8 @@ extern "C" int b2l_post_norm_residual(void* residual_f32, void* act, const void*
   if (rows == 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
   B2L_DISPATCH_FLOAT(dtype, "post_norm_residual", {
-    b2l_launch(post_norm_residual_kernel<T>, dim3((unsigned)rows), dim3(256), (size_t)0, st, (float*)residual_f32,
-               (T*)act, (const T*)y, (const T*)weight, (const T*)layer_scale, (const T*)next_weight, n, y_row_stride,
-               eps, weight_offset, norm_kind, next_norm_kind);
+    launch_post_norm<T>((float*)residual_f32, (T*)act, (const T*)y, (const T*)weight, (const T*)layer_scale,
+                        (const T*)next_weight, rows, n, y_row_stride, eps, weight_offset, norm_kind, next_norm_kind, st);
   });
   B2L_LAUNCH_CHECK();
   return B2L_OK;

@@ -494,7 +494,7 @@ def random_pesivik_tensors(cfg: LayeredConfig, seed: int = 0) -> dict[str, torch
     return out
 
 
-_PESIVIK_SOURCES = ("gemm_dense", "gemm_simt", "residual_stream", "attention_sink", "latent_attention", "moe_routing",
-                    "elementwise")
+_PESIVIK_SOURCES = ("gemm_dense", "gemm_simt", "gemm_rows_mma", "residual_stream", "attention_sink", "latent_attention",
+                    "moe_routing", "elementwise")
 register(Architecture("Pesivik", parse_pesivik_config, map_pesivik_weights, LayeredDecoder, ragged_steps=True,
                       sources=_PESIVIK_SOURCES))

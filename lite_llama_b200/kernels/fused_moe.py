@@ -195,8 +195,9 @@ def grouped_experts(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, w
                     ids: torch.Tensor, addend: torch.Tensor | None = None, activation: str = "gelu") -> torch.Tensor:
     """``sum_k weights[t, k] * W_down[e] act(W_up[e] x[t]) (+ addend[t])`` over each token's chosen experts
     ``e = ids[t, k]``: ungated two-matrix experts, ``w_up [E, ff, h]``, ``w_down [E, h, ff]``.  Slots are sorted by
-    expert (``moe_align_block_size``), both products run grouped on the CUDA cores with the activation in the first
-    one's epilogue and the fp32 routing weight in the second's; fp16 / bf16 / true fp32.  The gated (SwiGLU) experts of
+    expert (``moe_align_block_size``), both products run grouped (``mma.sync`` tiles for aligned 16-bit operands, the
+    CUDA cores for true fp32 and odd shapes) with the activation in the first one's epilogue and the fp32 routing weight
+    in the second's.  The gated (SwiGLU) experts of
     the reference's family are ``fused_moe``."""
     require_cuda(x, w_up, w_down, weights, ids, addend)
     if activation != "gelu":
@@ -207,22 +208,31 @@ def grouped_experts(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, w
     num_experts, ff, _ = w_up.shape
     top_k = ids.shape[1]
     L = lib()
-    block = L.b2l_moe_gemm_simt_block()
-    sorted_ids, expert_ids, num_post = moe_align_block_size(ids, block, num_experts)
-    slots = tokens * top_k
     code = float_code(x, "x")
     if x.stride(-1) != 1:
         x = x.contiguous()
     w_up, w_down = w_up.contiguous(), w_down.contiguous()
+    slots = tokens * top_k
     mid = torch.empty((slots, ff), dtype=x.dtype, device=x.device)
-    check(L.b2l_moe_gemm_simt(mid.data_ptr(), x.data_ptr(), w_up.data_ptr(), None, sorted_ids.data_ptr(),
-                              expert_ids.data_ptr(), num_post.data_ptr(), sorted_ids.numel(), slots, top_k, ff, hidden,
-                              x.stride(0), mid.stride(0), 1, code, stream_handle()))
     expanded = torch.empty((slots, hidden), dtype=x.dtype, device=x.device)
     flat_w = weights.reshape(-1).contiguous()
-    check(L.b2l_moe_gemm_simt(expanded.data_ptr(), mid.data_ptr(), w_down.data_ptr(), flat_w.data_ptr(),
-                              sorted_ids.data_ptr(), expert_ids.data_ptr(), num_post.data_ptr(), sorted_ids.numel(),
-                              slots, 1, hidden, ff, mid.stride(0), expanded.stride(0), 0, code, stream_handle()))
+    # 16-bit operands with 16-byte aligned rows run on the tensor cores (64-slot blocks, 16 when an expert sees few
+    # slots), everything else on the CUDA cores; the result of a slot does not depend on the block size
+    tensor = bool(L.b2l_rows_gemm_mma_ok(x.data_ptr(), w_up.data_ptr(), hidden, x.stride(0), 0, code)) and \
+        bool(L.b2l_rows_gemm_mma_ok(mid.data_ptr(), w_down.data_ptr(), ff, mid.stride(0), 0, code))
+    block = (64 if slots > 16 * num_experts else 16) if tensor else L.b2l_moe_gemm_simt_block()
+    sorted_ids, expert_ids, num_post = moe_align_block_size(ids, block, num_experts)
+    common = (sorted_ids.data_ptr(), expert_ids.data_ptr(), num_post.data_ptr(), sorted_ids.numel(), slots)
+    if tensor:
+        check(L.b2l_moe_gemm_mma(mid.data_ptr(), x.data_ptr(), w_up.data_ptr(), None, *common, top_k, block, ff, hidden,
+                                 x.stride(0), mid.stride(0), 1, code, stream_handle()))
+        check(L.b2l_moe_gemm_mma(expanded.data_ptr(), mid.data_ptr(), w_down.data_ptr(), flat_w.data_ptr(), *common, 1,
+                                 block, hidden, ff, mid.stride(0), expanded.stride(0), 0, code, stream_handle()))
+    else:
+        check(L.b2l_moe_gemm_simt(mid.data_ptr(), x.data_ptr(), w_up.data_ptr(), None, *common, top_k, ff, hidden,
+                                  x.stride(0), mid.stride(0), 1, code, stream_handle()))
+        check(L.b2l_moe_gemm_simt(expanded.data_ptr(), mid.data_ptr(), w_down.data_ptr(), flat_w.data_ptr(), *common, 1,
+                                  hidden, ff, mid.stride(0), expanded.stride(0), 0, code, stream_handle()))
     out = torch.empty((tokens, hidden), dtype=x.dtype, device=x.device)
     check(L.b2l_moe_sum(out.data_ptr(), expanded.data_ptr(), ptr(addend), tokens, hidden, top_k, code, stream_handle()))
     return out

@@ -40,11 +40,15 @@ def rope_heads(dst: torch.Tensor, dst_head_stride: int, src: torch.Tensor, src_h
 def head_linear(out: torch.Tensor, out_head_stride: int, x: torch.Tensor, x_head_stride: int, w: torch.Tensor,
                 gate: torch.Tensor | None = None) -> None:
     """``out[t, h, :n] = w[h] @ x[t, h, :k]`` for ``w [heads, n, k]``; optional ``gate [T, >= heads]``:
-    ``out[t, h] *= sigmoid(gate[t, h])``.  fp32 sums in ascending k, any dtype of the layer-list models."""
+    ``out[t, h] *= sigmoid(gate[t, h])``.  fp32 sums in ascending k, any dtype of the layer-list models (16-bit aligned
+    operands: ``mma.sync`` tiles, csrc/gemm_rows_mma.cu; fp32 or odd shapes: CUDA cores, csrc/gemm_simt.cu)."""
     require_cuda(out, x, w, gate)
     heads, n, k = w.shape
     if w.dtype != x.dtype or not w.is_contiguous() or x.stride(-1) != 1 or out.stride(-1) != 1:
         raise ValueError("head_linear: bad layout")
-    check(lib().b2l_head_linear(out.data_ptr(), out.stride(0), out_head_stride, x.data_ptr(), x.stride(0), x_head_stride,
-                                w.data_ptr(), ptr(gate), gate.stride(0) if gate is not None else 0, x.shape[0], heads,
-                                n, k, float_code(x, "x"), stream_handle()))
+    L, code = lib(), float_code(x, "x")
+    # 16-bit operands with 16-byte aligned rows run on the tensor cores, everything else on the CUDA cores
+    fn = L.b2l_head_linear_mma if L.b2l_rows_gemm_mma_ok(x.data_ptr(), w.data_ptr(), k, x.stride(0), x_head_stride, code) \
+        else L.b2l_head_linear
+    check(fn(out.data_ptr(), out.stride(0), out_head_stride, x.data_ptr(), x.stride(0), x_head_stride, w.data_ptr(),
+             ptr(gate), gate.stride(0) if gate is not None else 0, x.shape[0], heads, n, k, code, stream_handle()))
