@@ -424,11 +424,13 @@ def pesivik_kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) 
     rows_p = table[:, :ctx].reshape(-1).contiguous()
     pos_p = i32(list(range(prompt)) * batch)
     wq, wkv = rnd(qr, s=0.1) + 1, rnd(kr, s=0.1) + 1
+    cs = K.rope_table(pos_p, rot, 500000.0)
+    add("rope_table (once per step)", None, lambda: K.rope_table(pos_p, rot, 500000.0), nbytes=T * (4 + rot * 4))
     upool = rnd(batch * (ctx + 1), 2 * G * UD, dt=f16, s=0.5)
     uqkv = rnd(T, (H + 2 * G) * UD, dt=f16, s=0.5)
     cos = rnd(batch, prompt, UD, dt=f16)
     add("latent_prepare", "rope_kv_write",
-        lambda: K.latent_prepare(proj, pool, rows_p, pos_p, wq, wkv, qr, kr, rot, rot, 500000.0, 1e-5),
+        lambda: K.latent_prepare(proj, pool, rows_p, cs, wq, wkv, qr, kr, rot, rot, 1e-5),
         nbytes=T * ((2 * qr + kr + rot) * es + D * es),
         like_fn=lambda: K.rope_kv_write(uqkv[:, :H * UD].view(T, H, UD), uqkv[:, H * UD:(H + G) * UD].view(T, G, UD),
                                         uqkv[:, (H + G) * UD:].view(T, G, UD), cos, cos, rows_p, upool.view(-1, 2 * G, UD), batch, prompt),
@@ -442,7 +444,7 @@ def pesivik_kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) 
         lambda: K.head_linear(qa, D, q, dim + rot, ukt), flops=2 * T * H * kr * dim,
         like_fn=lambda: K.linear(dense_x, dense_w))
     add("rope_heads (queries' rotated parts)", None,
-        lambda: K.rope_heads(qa[:, kr:], D, q[:, dim:], dim + rot, pos_p, H, rot, rot, 500000.0), nbytes=T * H * rot * 2 * es)
+        lambda: K.rope_heads(qa[:, kr:], D, q[:, dim:], dim + rot, cs, H, rot, rot), nbytes=T * H * rot * 2 * es)
     lat = rnd(T, H * kr, s=0.5)
     o = torch.empty(T, H * vdim, dtype=dtype, device=dev)
     uv = rnd(H, vdim, kr, s=0.1)

@@ -308,25 +308,32 @@ int b2l_moe_gemm_mma(void* c, const void* a, const void* w, const void* slot_wei
                      const void* expert_ids, const void* num_tokens_post_padded, int64_t em, int64_t num_valid_slots,
                      int top_k, int block_size, int64_t n, int64_t k, int64_t a_row_stride, int64_t c_row_stride,
                      int act, int dtype, void* stream);
-/* Router product + sigmoid scores + selection bias + group-limited top-k in one launch (csrc/moe_routing.cu):
+/* Sigmoid scores + selection bias + group-limited top-k (csrc/moe_routing.cu); the router product is done inside
+ * unless logits_f32 [tokens, experts] (nullable) brings it:
  * z = router_w . x in fp32, s = sigmoid(z), choice = s + bias (nullable); `groups` equal runs of neighbouring experts,
  * group score = sum of its two largest choice scores, only the `keep` best groups are eligible; the top_k largest
  * choice scores win; weights_f32 [tokens, top_k] = s of the winners / (their sum + 1e-20); ids_i32 [tokens, top_k]. */
 int b2l_moe_route_sigmoid_groups(void* weights_f32, void* ids_i32, const void* x, int64_t x_row_stride,
-                                 const void* router_w, const void* bias, int64_t tokens, int num_experts, int64_t k,
-                                 int top_k, int groups, int keep, int dtype, void* stream);
-/* Latent attention, per token of the fused down-projection row [a: q_rank | b: kv_rank | r: rot_dim | ...]
- * (csrc/latent_attention.cu): a <- rmsnorm(a) * q_norm_weight in place; pool row kv_rows[t] =
- * [rmsnorm(b) * kv_norm_weight | r with its first rot_dims entries rotated by pos[t]]. */
+                                 const void* router_w, const void* bias, const void* logits_f32, int64_t tokens,
+                                 int num_experts, int64_t k, int top_k, int groups, int keep, int dtype, void* stream);
+/* y_f32[m, n] = x[m, k] . w[n, k]^T: 16-bit operands on the tensor cores, the fp32 sums stored unrounded (router
+ * logits); operands as b2l_rows_gemm_mma_ok asks. */
+int b2l_linear_f32out_mma(void* y_f32, const void* x, const void* w, int64_t m, int64_t n, int64_t k,
+                          int64_t x_row_stride, int64_t y_row_stride, int dtype, void* stream);
+/* cos_sin_f32[t] = [cos(pos[t] f_i), i < rot_dims / 2 | sin(pos[t] f_i)] with f_i = base^(-2i / rot_dims), angles in
+ * fp64 (csrc/latent_attention.cu); one table per step serves every layer with these rotary constants. */
+int b2l_rope_table(void* cos_sin_f32, const void* pos_i32, int64_t tokens, int rot_dims, float rot_base, void* stream);
+/* Latent attention, per token of the fused down-projection row [a: q_rank | b: kv_rank | r: rot_dim | ...]:
+ * a <- rmsnorm(a) * q_norm_weight in place; pool row kv_rows[t] = [rmsnorm(b) * kv_norm_weight | r with its first
+ * rot_dims entries rotated by the token's row of cos_sin_f32 (entry i pairs with i + rot_dims / 2)]. */
 int b2l_latent_prepare(void* proj, int64_t proj_row_stride, void* pool, int64_t pool_row_stride,
-                       const void* kv_rows_i32, const void* pos_i32, const void* q_norm_weight,
+                       const void* kv_rows_i32, const void* cos_sin_f32, const void* q_norm_weight,
                        const void* kv_norm_weight, int64_t tokens, int q_rank, int kv_rank, int rot_dim, int rot_dims,
-                       float rot_base, float eps, int dtype, void* stream);
-/* dst[t, h, :width] = src[t, h, :width], the first rot_dims entries rotated by pos[t] (entry i pairs with
- * i + rot_dims / 2, angle pos * base^(-2i / rot_dims)). */
+                       float eps, int dtype, void* stream);
+/* dst[t, h, :width] = src[t, h, :width], the first rot_dims entries rotated by the token's row of cos_sin_f32. */
 int b2l_rope_heads(void* dst, int64_t dst_row_stride, int dst_head_stride, const void* src, int64_t src_row_stride,
-                   int src_head_stride, const void* pos_i32, int64_t tokens, int heads, int width, int rot_dims,
-                   float rot_base, int dtype, void* stream);
+                   int src_head_stride, const void* cos_sin_f32, int64_t tokens, int heads, int width, int rot_dims,
+                   int dtype, void* stream);
 
 /* Short causal convolution per channel + SiLU over a ragged step, and the slot's tail (last taps-1 inputs) update.
  * in: [tokens, >= channels] with row stride; weight [channels, taps] (last column = current token); tail

@@ -77,8 +77,27 @@ def load() -> ctypes.CDLL:
             raise LibraryMissing(f"{LIB_PATH.name} does not export {name}; rebuild the library") from e
         fn.restype = _CTYPES[ret]
         fn.argtypes = [_CTYPES[a] for a in args]
-    _lib = lib
-    return lib
+    _lib = _Declared(lib)
+    return _lib
+
+
+class UndeclaredSymbol(LibraryMissing, AttributeError):
+    pass
+
+
+class _Declared:
+    """The library behind the names the header declares.  ctypes would hand out ANY exported symbol with its default
+    signature (every argument a C int, so 64-bit pointers are cut in half); a symbol without a parsed prototype is an
+    error here instead."""
+
+    def __init__(self, lib: ctypes.CDLL) -> None:
+        self._lib = lib
+
+    def __getattr__(self, name: str):
+        fn = self._lib.__dict__.get(name)
+        if fn is None:
+            raise UndeclaredSymbol(f"{HEADER_PATH.name} declares no {name}: the binding would call it without a prototype")
+        return fn
 
 
 def _missing(name: str):

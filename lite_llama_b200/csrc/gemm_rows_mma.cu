@@ -22,6 +22,7 @@ struct RowsArgs {
   // grouped map
   const float* slot_weight; const int* sorted_ids; const int* expert_ids; const int* num_post;
   int64_t num_valid; int top_k, act;
+  int out_f32;                 // per-head map only: y is fp32 (router logits: 16-bit operands, 32-bit sums kept as they are)
 };
 
 __device__ __forceinline__ void cp16(uint32_t saddr, const void* g) {
@@ -40,7 +41,7 @@ __global__ void __launch_bounds__(128) rows_gemm_mma_kernel(RowsArgs a) {
   __shared__ __align__(16) T As[2][BM][kPitch];
   __shared__ __align__(16) T Ws[2][kBN][kPitch];
   __shared__ const T* arow[BM];
-  __shared__ T* crow[BM];
+  __shared__ void* crow[BM];
   __shared__ float mult[BM];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t n0 = (int64_t)blockIdx.x * kBN;
@@ -53,7 +54,7 @@ __global__ void __launch_bounds__(128) rows_gemm_mma_kernel(RowsArgs a) {
       const int64_t slot = a.sorted_ids[b0 + tid];
       const bool ok = slot < a.num_valid;
       arow[tid] = ok ? (const T*)a.x + (slot / a.top_k) * a.xs : nullptr;
-      crow[tid] = ok ? (T*)a.y + slot * a.ys : nullptr;
+      crow[tid] = ok ? (void*)((T*)a.y + slot * a.ys) : nullptr;
       mult[tid] = (ok && a.slot_weight) ? a.slot_weight[slot] : 1.0f;
     }
   } else {
@@ -63,7 +64,8 @@ __global__ void __launch_bounds__(128) rows_gemm_mma_kernel(RowsArgs a) {
       const int64_t row = (int64_t)blockIdx.y * BM + tid;
       const bool ok = row < a.m;
       arow[tid] = ok ? (const T*)a.x + row * a.xs + h * a.xh : nullptr;
-      crow[tid] = ok ? (T*)a.y + row * a.ys + h * a.yh : nullptr;
+      const int64_t off = row * a.ys + h * a.yh;
+      crow[tid] = ok ? (a.out_f32 ? (void*)((float*)a.y + off) : (void*)((T*)a.y + off)) : nullptr;
       mult[tid] = (ok && a.gate) ? 1.0f / (1.0f + expf(-to_f32(((const T*)a.gate)[row * a.gs + h]))) : 1.0f;
     }
   }
@@ -111,9 +113,19 @@ __global__ void __launch_bounds__(128) rows_gemm_mma_kernel(RowsArgs a) {
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     const int r = wm * 16 + gq + half * 8;
-    T* dst = crow[r];
-    if (!dst) continue;
+    if (!crow[r]) continue;
     const float g = mult[r];
+    if (!GROUPED && a.out_f32) {
+      float* d32 = (float*)crow[r];
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const int64_t col = n0 + wn * (NT * 8) + j * 8 + 2 * tq;
+        if (col < a.n) d32[col] = acc[j][half * 2] * g;
+        if (col + 1 < a.n) d32[col + 1] = acc[j][half * 2 + 1] * g;
+      }
+      continue;
+    }
+    T* dst = (T*)crow[r];
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
       const int64_t col = n0 + wn * (NT * 8) + j * 8 + 2 * tq;
@@ -189,6 +201,24 @@ extern "C" int b2l_moe_gemm_mma(void* c, const void* a_in, const void* w, const 
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == B2L_F16) launch_rows<__half, 1>(a, block_size, grid, st);
   else launch_rows<__nv_bfloat16, 1>(a, block_size, grid, st);
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}
+
+/* y_f32[m, n] = x[m, k] . w[n, k]^T with 16-bit operands and the fp32 tensor-core sums stored unrounded. */
+extern "C" int b2l_linear_f32out_mma(void* y_f32, const void* x, const void* w, int64_t m, int64_t n, int64_t k,
+                                     int64_t x_row_stride, int64_t y_row_stride, int dtype, void* stream) {
+  B2L_REQUIRE(y_f32 && x && w, "linear_f32out_mma: null pointer");
+  B2L_REQUIRE(m >= 0 && n > 0, "linear_f32out_mma: bad shape");
+  B2L_REQUIRE(b2l_rows_gemm_mma_ok(x, w, k, x_row_stride, 0, dtype), "linear_f32out_mma: operands not aligned");
+  if (m == 0) return B2L_OK;
+  RowsArgs a = {};
+  a.x = x; a.w = w; a.y = y_f32; a.n = n; a.k = k; a.xs = x_row_stride; a.ys = y_row_stride; a.m = m; a.out_f32 = 1;
+  const int bm = m <= 16 ? 16 : 64;
+  const dim3 grid((unsigned)cdiv64(n, kBN), (unsigned)cdiv64(m, bm), 1u);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == B2L_F16) launch_rows<__half, 0>(a, bm, grid, st);
+  else launch_rows<__nv_bfloat16, 0>(a, bm, grid, st);
   B2L_LAUNCH_CHECK();
   return B2L_OK;
 }

@@ -8,10 +8,13 @@
 //   pool row  = [ b / rms(b) * wkv | rotate(r, pos) ]
 //
 //   rope_heads: dst[t, h, :width] = src[t, h, :width] with the first `rot_dims` entries rotated by the token's position
-//               (entry i pairs with entry i + rot_dims/2; angle pos * base^(-2i/rot_dims)); the rest is copied.
+//               (entry i pairs with entry i + rot_dims/2); the rest is copied.
+//
+//   rope_table: cs[t] = [cos(pos_t f_i), i < rot_dims/2 | sin(pos_t f_i)], f_i = base^(-2i/rot_dims), once per step: every
+//               layer with the same rotary constants reads the same table.
 //
 // Statistics and the rotation are fp32; the angle and its sine / cosine are evaluated in fp64 (a position of a few
-// thousand times a frequency near 1 loses the low bits of the angle in fp32).
+// thousand times a frequency near 1 loses the low bits of the angle in fp32) and stored as fp32.
 #include "common.cuh"
 
 namespace {
@@ -24,14 +27,28 @@ __device__ __forceinline__ void pair_angle(int pos, int i, int dims, double log2
   c = (float)cd; s = (float)sd;
 }
 
+__global__ void rope_table_kernel(float* __restrict__ cs, const int* __restrict__ pos, int64_t tokens, int dims,
+                                  double log2_base) {
+  pdl_prologue();
+  const int half = dims / 2;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= tokens * half) return;
+  const int64_t t = i / half;
+  const int k = (int)(i - t * half);
+  float c, s;
+  pair_angle(pos[t], k, dims, log2_base, c, s);
+  cs[t * dims + k] = c;
+  cs[t * dims + half + k] = s;
+}
+
 // One WARP per token (four tokens per CTA): the two statistics are warp reductions, nothing waits on a barrier.
 template <typename T>
 __global__ void __launch_bounds__(128) latent_prepare_kernel(T* __restrict__ proj, int64_t stride, T* __restrict__ pool,
                                                              int64_t pool_stride, const int* __restrict__ rows,
-                                                             const int* __restrict__ pos, const T* __restrict__ wq,
-                                                             const T* __restrict__ wkv, int64_t tokens, int q_rank,
-                                                             int kv_rank, int rot_dim, int rot_dims, double log2_base,
-                                                             float eps) {
+                                                             const float* __restrict__ cs_table,
+                                                             const T* __restrict__ wq, const T* __restrict__ wkv,
+                                                             int64_t tokens, int q_rank, int kv_rank, int rot_dim,
+                                                             int rot_dims, float eps) {
   pdl_prologue();
   const int lane = threadIdx.x & 31;
   const int64_t t = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -48,10 +65,10 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(T* __restrict__ pro
   for (int i = lane; i < kv_rank; i += 32) { const float v = to_f32(b[i]); ss = fmaf(v, v, ss); }
   rstd = 1.0f / sqrtf(warp_reduce_sum(ss) / (float)kv_rank + eps);
   for (int i = lane; i < kv_rank; i += 32) dst[i] = from_f32<T>(to_f32(b[i]) * rstd * to_f32(wkv[i]));
-  const int half = rot_dims / 2, p = pos[t];
+  const int half = rot_dims / 2;
+  const float* cs = cs_table + t * rot_dims;
   for (int i = lane; i < half; i += 32) {
-    float c, s;
-    pair_angle(p, i, rot_dims, log2_base, c, s);
+    const float c = cs[i], s = cs[half + i];
     const float u = to_f32(r[i]), v = to_f32(r[i + half]);
     dst[kv_rank + i] = from_f32<T>(u * c - v * s);
     dst[kv_rank + i + half] = from_f32<T>(v * c + u * s);
@@ -62,18 +79,14 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(T* __restrict__ pro
 template <typename T>
 __global__ void __launch_bounds__(128) rope_heads_kernel(T* __restrict__ dst, int64_t dst_stride, int dst_head_stride,
                                                          const T* __restrict__ src, int64_t src_stride,
-                                                         int src_head_stride, const int* __restrict__ pos,
-                                                         int64_t tokens, int heads, int width, int rot_dims,
-                                                         double log2_base) {
+                                                         int src_head_stride, const float* __restrict__ cs_table,
+                                                         int64_t tokens, int heads, int width, int rot_dims) {
   pdl_prologue();
-  extern __shared__ float cs_all[];                  // per warp: [half] cos, [half] sin of its token
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t t = (int64_t)blockIdx.x * 4 + warp;
   if (t >= tokens) return;
-  const int half = rot_dims / 2, p = pos[t];
-  float* cs = cs_all + warp * 2 * (half > 0 ? half : 1);
-  for (int i = lane; i < half; i += 32) pair_angle(p, i, rot_dims, log2_base, cs[i], cs[half + i]);
-  __syncwarp();
+  const int half = rot_dims / 2;
+  const float* cs = cs_table + t * rot_dims;
   const T* s = src + t * src_stride;
   T* d = dst + t * dst_stride;
   for (int i = lane; i < heads * width; i += 32) {
@@ -89,40 +102,50 @@ __global__ void __launch_bounds__(128) rope_heads_kernel(T* __restrict__ dst, in
 
 }  // namespace
 
+extern "C" int b2l_rope_table(void* cos_sin_f32, const void* pos_i32, int64_t tokens, int rot_dims, float rot_base,
+                              void* stream) {
+  B2L_REQUIRE(cos_sin_f32 && pos_i32, "rope_table: null pointer");
+  B2L_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_base > 0.f, "rope_table: bad constants");
+  if (tokens <= 0 || rot_dims == 0) return B2L_OK;
+  const int64_t total = tokens * (rot_dims / 2);
+  b2l_launch(rope_table_kernel, dim3((unsigned)cdiv64(total, 128)), dim3(128), (size_t)0, (cudaStream_t)stream,
+             (float*)cos_sin_f32, (const int*)pos_i32, tokens, rot_dims, log2((double)rot_base));
+  B2L_LAUNCH_CHECK();
+  return B2L_OK;
+}
+
 extern "C" int b2l_latent_prepare(void* proj, int64_t proj_row_stride, void* pool, int64_t pool_row_stride,
-                                  const void* kv_rows_i32, const void* pos_i32, const void* q_norm_weight,
+                                  const void* kv_rows_i32, const void* cos_sin_f32, const void* q_norm_weight,
                                   const void* kv_norm_weight, int64_t tokens, int q_rank, int kv_rank, int rot_dim,
-                                  int rot_dims, float rot_base, float eps, int dtype, void* stream) {
-  B2L_REQUIRE(proj && pool && kv_rows_i32 && pos_i32 && q_norm_weight && kv_norm_weight, "latent_prepare: null pointer");
+                                  int rot_dims, float eps, int dtype, void* stream) {
+  B2L_REQUIRE(proj && pool && kv_rows_i32 && q_norm_weight && kv_norm_weight, "latent_prepare: null pointer");
   B2L_REQUIRE(q_rank > 0 && kv_rank > 0 && rot_dim >= 0 && rot_dims >= 0 && rot_dims <= rot_dim && rot_dims % 2 == 0,
               "latent_prepare: bad shape (q_rank %d, kv_rank %d, rot_dim %d, rot_dims %d)", q_rank, kv_rank, rot_dim, rot_dims);
-  B2L_REQUIRE(rot_base > 0.f, "latent_prepare: rotary base must be positive");
+  B2L_REQUIRE(cos_sin_f32 || rot_dims == 0, "latent_prepare: no rotation table");
   if (tokens <= 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  const double l2b = log2((double)rot_base);
   B2L_DISPATCH_FLOAT(dtype, "latent_prepare", {
     b2l_launch(latent_prepare_kernel<T>, dim3((unsigned)cdiv64(tokens, 4)), dim3(128), (size_t)0, st, (T*)proj,
-               proj_row_stride, (T*)pool, pool_row_stride, (const int*)kv_rows_i32, (const int*)pos_i32,
-               (const T*)q_norm_weight, (const T*)kv_norm_weight, tokens, q_rank, kv_rank, rot_dim, rot_dims, l2b, eps);
+               proj_row_stride, (T*)pool, pool_row_stride, (const int*)kv_rows_i32, (const float*)cos_sin_f32,
+               (const T*)q_norm_weight, (const T*)kv_norm_weight, tokens, q_rank, kv_rank, rot_dim, rot_dims, eps);
   });
   B2L_LAUNCH_CHECK();
   return B2L_OK;
 }
 
 extern "C" int b2l_rope_heads(void* dst, int64_t dst_row_stride, int dst_head_stride, const void* src,
-                              int64_t src_row_stride, int src_head_stride, const void* pos_i32, int64_t tokens,
-                              int heads, int width, int rot_dims, float rot_base, int dtype, void* stream) {
-  B2L_REQUIRE(dst && src && pos_i32, "rope_heads: null pointer");
-  B2L_REQUIRE(heads > 0 && width >= 0 && rot_dims >= 0 && rot_dims <= width && rot_dims % 2 == 0 && rot_base > 0.f,
+                              int64_t src_row_stride, int src_head_stride, const void* cos_sin_f32, int64_t tokens,
+                              int heads, int width, int rot_dims, int dtype, void* stream) {
+  B2L_REQUIRE(dst && src, "rope_heads: null pointer");
+  B2L_REQUIRE(heads > 0 && width >= 0 && rot_dims >= 0 && rot_dims <= width && rot_dims % 2 == 0,
               "rope_heads: bad shape (heads %d, width %d, rot_dims %d)", heads, width, rot_dims);
+  B2L_REQUIRE(cos_sin_f32 || rot_dims == 0, "rope_heads: no rotation table");
   if (tokens <= 0 || width == 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  const double l2b = log2((double)rot_base);
-  const size_t smem = (size_t)4 * (rot_dims > 0 ? rot_dims : 2) * sizeof(float);
   B2L_DISPATCH_FLOAT(dtype, "rope_heads", {
-    b2l_launch(rope_heads_kernel<T>, dim3((unsigned)cdiv64(tokens, 4)), dim3(128), smem, st, (T*)dst, dst_row_stride,
-               dst_head_stride, (const T*)src, src_row_stride, src_head_stride, (const int*)pos_i32, tokens, heads, width,
-               rot_dims, l2b);
+    b2l_launch(rope_heads_kernel<T>, dim3((unsigned)cdiv64(tokens, 4)), dim3(128), (size_t)0, st, (T*)dst, dst_row_stride,
+               dst_head_stride, (const T*)src, src_row_stride, src_head_stride, (const float*)cos_sin_f32, tokens, heads,
+               width, rot_dims);
   });
   B2L_LAUNCH_CHECK();
   return B2L_OK;

@@ -140,7 +140,8 @@ __global__ void moe_route_kernel(const T* __restrict__ logits, int64_t row_strid
   }
 }
 
-// Sigmoid router with a selection bias and group-limited choice, router product included (one CTA per token):
+// Sigmoid router with a selection bias and group-limited choice (one CTA per token; the router product is done here,
+// or comes as fp32 logits from a GEMM, in which case the CTA is a single warp):
 //   z = W_r . x (fp32 sums),  s = sigmoid(z),  choice = s + bias
 //   the experts form `groups` equal runs of neighbours; a group's score = the sum of its two largest choice scores;
 //   only experts of the `keep` best groups can be chosen; the `top_k` largest choice scores among them win
@@ -148,7 +149,8 @@ __global__ void moe_route_kernel(const T* __restrict__ logits, int64_t row_strid
 template <typename T>
 __global__ void __launch_bounds__(128) moe_route_sigmoid_kernel(const T* __restrict__ x, int64_t xs,
                                                                 const T* __restrict__ wr, const T* __restrict__ bias,
-                                                                int num_experts, int k, int top_k, int groups, int keep,
+                                                                const float* __restrict__ logits, int num_experts,
+                                                                int k, int top_k, int groups, int keep,
                                                                 float* __restrict__ out_w, int* __restrict__ out_ids) {
   pdl_prologue();
   extern __shared__ float rs[];
@@ -157,6 +159,13 @@ __global__ void __launch_bounds__(128) moe_route_sigmoid_kernel(const T* __restr
   float* gs = ch + num_experts;                  // [groups]
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const T* xr = x + (int64_t)t * xs;
+  if (logits) {                                  // the router product was done by a GEMM: fp32 logits [tokens, E]
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+      const float s = 1.0f / (1.0f + expf(-logits[(int64_t)t * num_experts + e]));
+      sc[e] = s;
+      ch[e] = s + (bias ? to_f32(bias[e]) : 0.f);
+    }
+  } else
   for (int e = warp; e < num_experts; e += nw) {
     const T* w = wr + (int64_t)e * k;
     float acc = 0.f;
@@ -286,13 +295,14 @@ extern "C" int b2l_moe_route_topk(void* topk_weights, void* topk_ids_i64, const 
   return B2L_OK;
 }
 
-/* Router product + sigmoid scores + selection bias + group-limited top-k in one launch (fp32 throughout):
- * x [tokens, k] and router_w [experts, k] in dtype, bias [experts] in dtype (nullable); weights_f32 [tokens, top_k],
- * ids_i32 [tokens, top_k].  groups must divide experts; keep <= groups. */
+/* Sigmoid scores + selection bias + group-limited top-k (fp32 throughout).  The router product is done here from
+ * x [tokens, k] and router_w [experts, k] in dtype, unless logits_f32 [tokens, experts] brings it; bias [experts] in
+ * dtype (nullable); weights_f32 [tokens, top_k], ids_i32 [tokens, top_k].  groups must divide experts; keep <= groups. */
 extern "C" int b2l_moe_route_sigmoid_groups(void* weights_f32, void* ids_i32, const void* x, int64_t x_row_stride,
-                                            const void* router_w, const void* bias, int64_t tokens, int num_experts,
-                                            int64_t k, int top_k, int groups, int keep, int dtype, void* stream) {
-  B2L_REQUIRE(weights_f32 && ids_i32 && x && router_w, "moe_route_sigmoid_groups: null pointer");
+                                            const void* router_w, const void* bias, const void* logits_f32,
+                                            int64_t tokens, int num_experts, int64_t k, int top_k, int groups, int keep,
+                                            int dtype, void* stream) {
+  B2L_REQUIRE(weights_f32 && ids_i32 && ((x && router_w) || logits_f32), "moe_route_sigmoid_groups: null pointer");
   B2L_REQUIRE(num_experts > 0 && k > 0 && k < (1ll << 31) && top_k >= 1 && top_k <= num_experts && groups >= 1 &&
                   num_experts % groups == 0 && keep >= 1 && keep <= groups &&
                   (int64_t)keep * (num_experts / groups) >= top_k,
@@ -302,9 +312,9 @@ extern "C" int b2l_moe_route_sigmoid_groups(void* weights_f32, void* ids_i32, co
   const size_t smem = (size_t)(2 * num_experts + 2 * groups) * sizeof(float);
   B2L_REQUIRE(smem <= 48 * 1024, "moe_route_sigmoid_groups: %d experts exceed the kernel's shared memory", num_experts);
   B2L_DISPATCH_FLOAT(dtype, "moe_route_sigmoid_groups", {
-    b2l_launch(moe_route_sigmoid_kernel<T>, dim3((unsigned)tokens), dim3(128), smem, st, (const T*)x, x_row_stride,
-               (const T*)router_w, (const T*)bias, num_experts, (int)k, top_k, groups, keep, (float*)weights_f32,
-               (int*)ids_i32);
+    b2l_launch(moe_route_sigmoid_kernel<T>, dim3((unsigned)tokens), dim3(logits_f32 ? 32 : 128), smem, st, (const T*)x,
+               x_row_stride, (const T*)router_w, (const T*)bias, (const float*)logits_f32, num_experts, (int)k, top_k,
+               groups, keep, (float*)weights_f32, (int*)ids_i32);
   });
   B2L_LAUNCH_CHECK();
   return B2L_OK;

@@ -193,15 +193,28 @@ __global__ void rmsnorm_from_f32_kernel(T* __restrict__ o, const float* __restri
     o[(int64_t)blockIdx.x * n + i] = from_f32<T>((x[i] - mean) * rstd * (offset + to_f32(w[i])));
 }
 
+__device__ __forceinline__ float gelu_f(float v, int tanh_form) {
+  return tanh_form ? 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)))
+                   : 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
+}
+
+// 16-byte accesses over the aligned body (`vec` = 1), scalars over the tail or everything
 template <typename T>
-__global__ void gelu_kernel(T* __restrict__ o, const T* __restrict__ x, int64_t total, int tanh_form) {
+__global__ void gelu_kernel(T* __restrict__ o, const T* __restrict__ x, int64_t total, int tanh_form, int vec) {
   pdl_prologue();
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const float v = to_f32(x[i]);
-    const float g = tanh_form ? 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)))
-                              : 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
-    o[i] = from_f32<T>(g);
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, step = (int64_t)gridDim.x * blockDim.x;
+  const int64_t chunks = vec ? total / VEC : 0;
+  for (int64_t c = tid; c < chunks; c += step) {
+    const uint4 raw = ldg_stream_128(x + c * VEC);
+    const T* e = reinterpret_cast<const T*>(&raw);
+    uint4 res;
+    T* r = reinterpret_cast<T*>(&res);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) r[j] = from_f32<T>(gelu_f(to_f32(e[j]), tanh_form));
+    stg_128(o + c * VEC, res);
   }
+  for (int64_t i = chunks * VEC + tid; i < total; i += step) o[i] = from_f32<T>(gelu_f(to_f32(x[i]), tanh_form));
 }
 
 template <typename T>
@@ -310,9 +323,11 @@ extern "C" int b2l_gelu(void* out, const void* x, int64_t total, int tanh_form, 
   B2L_REQUIRE(out && x, "gelu: null pointer");
   if (total <= 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  const unsigned grid = (unsigned)(cdiv64(total, 256) < 148 * 16 ? cdiv64(total, 256) : 148 * 16);
+  const int vec = ((uintptr_t)out % 16 == 0 && (uintptr_t)x % 16 == 0) ? 1 : 0;
+  const int64_t work = vec ? cdiv64(total, 4) : total;
+  const unsigned grid = (unsigned)(cdiv64(work, 256) < 148 * 16 ? cdiv64(work, 256) : 148 * 16);
   B2L_DISPATCH_FLOAT(dtype, "gelu", {
-    b2l_launch(gelu_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (T*)out, (const T*)x, total, tanh_form);
+    b2l_launch(gelu_kernel<T>, dim3(grid), dim3(256), (size_t)0, st, (T*)out, (const T*)x, total, tanh_form, vec);
   });
   B2L_LAUNCH_CHECK();
   return B2L_OK;

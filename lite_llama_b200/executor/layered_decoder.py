@@ -45,6 +45,7 @@ from ..kernels import (
     relu_squared,
     rmsnorm_from_f32,
     rope_heads,
+    rope_table,
     route_sigmoid_groups,
     sink_attention,
     softcap_to_f32,
@@ -101,6 +102,14 @@ class StepContext:
         self.table = table
         self.states = states
         self.v_first: torch.Tensor | None = None
+        self._rope: dict[tuple[int, float], torch.Tensor | None] = {}
+
+    def rope(self, rot_dims: int, rot_base: float) -> torch.Tensor | None:
+        """The step's [cos | sin] table for these rotary constants, built once and shared by the layers."""
+        key = (rot_dims, rot_base)
+        if key not in self._rope:
+            self._rope[key] = rope_table(self.batch.positions, rot_dims, rot_base)
+        return self._rope[key]
 
 
 def mamba2_mixer(li: int, spec: Mamba2Spec, w: dict[str, torch.Tensor], x: torch.Tensor, ctx: StepContext,
@@ -170,14 +179,14 @@ def latent_attention_mixer(li: int, spec: LatentAttentionSpec, w: dict[str, torc
     H, dim, rot, rank = spec.heads, spec.head_dim, spec.rot_dim, spec.kv_rank
     proj = linear(x, w["down"])
     pool = ctx.kv_buffer[li]
-    latent_prepare(proj, pool, b.kv_rows, b.positions, w["q_norm"], w["kv_norm"], spec.q_rank, rank, rot, spec.rot_dims,
-                   spec.rot_base, eps)
+    cos_sin = ctx.rope(spec.rot_dims, spec.rot_base)
+    latent_prepare(proj, pool, b.kv_rows, cos_sin, w["q_norm"], w["kv_norm"], spec.q_rank, rank, rot, spec.rot_dims, eps)
     q = linear(proj[:, :spec.q_rank], w["uq"])
     D = rank + rot
     qa = torch.empty((b.tokens, H * D), dtype=q.dtype, device=q.device)
     head_linear(qa, D, q, dim + rot, w["uk_t"])
     if rot:
-        rope_heads(qa[:, rank:], D, q[:, dim:], dim + rot, b.positions, H, rot, spec.rot_dims, spec.rot_base)
+        rope_heads(qa[:, rank:], D, q[:, dim:], dim + rot, cos_sin, H, rot, spec.rot_dims)
     lat = torch.empty((b.tokens, H * rank), dtype=q.dtype, device=q.device)
     common = (H, 1, D, rank, spec.scale, 0.0)
     if b.num_portions:

@@ -8,7 +8,7 @@ hand-written sm_100a CUDA from ``libb200lite.so`` on the current CUDA stream.
 from .flashattention2_nopad import flash_attention2_no_pad
 from .flashdecoding import flash_decoding
 from .fused_moe import fused_moe, grouped_experts, moe_align_block_size, route_sigmoid_groups, route_topk
-from .latent import head_linear, latent_prepare, rope_heads
+from .latent import head_linear, latent_prepare, rope_heads, rope_table
 from .linear import linear, linear_simt
 from .residual_stream import embed_positions, gelu, post_norm_residual, relu_squared, rmsnorm_from_f32, softcap_to_f32
 from .sink_attention import attn_prepare, sink_attention
@@ -32,6 +32,7 @@ __all__ = [
     "head_linear",
     "latent_prepare",
     "rope_heads",
+    "rope_table",
     "gelu",
     "softcap_to_f32",
     "linear",

@@ -170,7 +170,8 @@ def route_topk(router_logits: torch.Tensor, top_k: int, renormalize: bool = True
 @torch.no_grad()
 def route_sigmoid_groups(x: torch.Tensor, router_w: torch.Tensor, bias: torch.Tensor | None, top_k: int,
                          groups: int = 1, keep: int = 1):
-    """Sigmoid router with a selection bias and group-limited choice, the router product included, in one launch:
+    """Sigmoid router with a selection bias and group-limited choice (router product with fp32 results + one selection
+    launch; a single launch for shapes no GEMM takes):
     ``s = sigmoid(router_w @ x)`` in fp32; experts compete with ``s + bias``; they form ``groups`` runs of neighbours,
     a group scores the sum of its two best, only the ``keep`` best groups are eligible; the ``top_k`` winners' weights
     are their ``s`` over the winners' sum.  Returns ``(weights fp32 [T, k], ids int32 [T, k])``.  The reference's
@@ -182,11 +183,24 @@ def route_sigmoid_groups(x: torch.Tensor, router_w: torch.Tensor, bias: torch.Te
         raise ValueError("route_sigmoid_groups: router weight and bias must be in the activation dtype")
     tokens, k = x.shape
     e = router_w.shape[0]
+    router_w = router_w.contiguous()
     w = torch.empty((tokens, top_k), dtype=torch.float32, device=x.device)
     ids = torch.empty((tokens, top_k), dtype=torch.int32, device=x.device)
-    check(lib().b2l_moe_route_sigmoid_groups(w.data_ptr(), ids.data_ptr(), x.data_ptr(), x.stride(0),
-                                             router_w.contiguous().data_ptr(), ptr(bias), tokens, e, k, int(top_k),
-                                             int(groups), int(keep), float_code(x, "x"), stream_handle()))
+    L, code = lib(), float_code(x, "x")
+    # the router product as a GEMM with fp32 results where one fits (tensor cores for aligned 16-bit operands, the
+    # CUDA-core GEMM for true fp32); otherwise the selection kernel does the product itself
+    logits = None
+    if x.dtype == torch.float32:
+        from .linear import linear_simt
+
+        logits = linear_simt(x, router_w)
+    elif L.b2l_rows_gemm_mma_ok(x.data_ptr(), router_w.data_ptr(), k, x.stride(0), 0, code):
+        logits = torch.empty((tokens, e), dtype=torch.float32, device=x.device)
+        check(L.b2l_linear_f32out_mma(logits.data_ptr(), x.data_ptr(), router_w.data_ptr(), tokens, e, k, x.stride(0), e,
+                                      code, stream_handle()))
+    check(L.b2l_moe_route_sigmoid_groups(w.data_ptr(), ids.data_ptr(), x.data_ptr(), x.stride(0), router_w.data_ptr(),
+                                         ptr(bias), ptr(logits), tokens, e, k, int(top_k), int(groups), int(keep), code,
+                                         stream_handle()))
     return w, ids
 
 

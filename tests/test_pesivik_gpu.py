@@ -76,7 +76,7 @@ def test_gelu_forms_and_soft_cap(dtype, tol):
 @pytest.mark.parametrize("q_rank,kv_rank,rot_dim,rot_dims,heads", [(20, 12, 4, 4, 3), (16, 24, 8, 8, 2), (9, 5, 6, 2, 1),
                                                                    (8, 8, 0, 0, 2)])
 def test_latent_prepare_and_query_rotation(q_rank, kv_rank, rot_dim, rot_dims, heads):
-    from lite_llama_b200.kernels import latent_prepare, rope_heads
+    from lite_llama_b200.kernels import latent_prepare, rope_heads, rope_table
 
     T, eps, base = 6, 1e-4, 300.0
     cols = q_rank + kv_rank + rot_dim + heads
@@ -86,7 +86,9 @@ def test_latent_prepare_and_query_rotation(q_rank, kv_rank, rot_dim, rot_dims, h
     rows = [5, 0, 7, 2, 9, 1]
     pool = torch.full((10, kv_rank + rot_dim + 2), 9.0, device=DEV)
     dev = proj.to(DEV)
-    latent_prepare(dev, pool, _i32(rows), _i32(pos), wq.to(DEV), wkv.to(DEV), q_rank, kv_rank, rot_dim, rot_dims, base, eps)
+    cs = rope_table(_i32(pos), rot_dims, base)
+    assert (cs is None) == (rot_dims == 0)
+    latent_prepare(dev, pool, _i32(rows), cs, wq.to(DEV), wkv.to(DEV), q_rank, kv_rank, rot_dim, rot_dims, eps)
     p64 = O.f64(proj)
     _close(dev[:, :q_rank], np.stack([O.rms_norm(p64[t, :q_rank], O.f64(wq), eps) for t in range(T)]), 2e-6)
     _close(dev[:, q_rank:], p64[:, q_rank:], 0)                       # the rest of the row is left alone
@@ -100,7 +102,7 @@ def test_latent_prepare_and_query_rotation(q_rank, kv_rank, rot_dim, rot_dims, h
         q = torch.randn(T, heads * (dim + rot_dim))
         dst = torch.zeros(T, heads * (kv_rank + rot_dim), device=DEV)
         qd = q.to(DEV)
-        rope_heads(dst[:, kv_rank:], kv_rank + rot_dim, qd[:, dim:], dim + rot_dim, _i32(pos), heads, rot_dim, rot_dims, base)
+        rope_heads(dst[:, kv_rank:], kv_rank + rot_dim, qd[:, dim:], dim + rot_dim, cs, heads, rot_dim, rot_dims)
         for h in range(heads):
             ref = np.stack([O.rotate(O.f64(q[t, h * (dim + rot_dim) + dim:(h + 1) * (dim + rot_dim)]), pos[t], rot_dims, base)
                             for t in range(T)])
