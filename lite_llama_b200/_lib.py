@@ -93,6 +93,11 @@ class _Declared:
     def __init__(self, lib: ctypes.CDLL) -> None:
         self._lib = lib
 
+    @property
+    def cdll(self) -> ctypes.CDLL:
+        """The raw library, for debug symbols outside the declared ABI (the caller sets their prototypes)."""
+        return self._lib
+
     def __getattr__(self, name: str):
         fn = self._lib.__dict__.get(name)
         if fn is None:

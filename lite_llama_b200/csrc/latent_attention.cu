@@ -76,27 +76,30 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(T* __restrict__ pro
   for (int i = 2 * half + lane; i < rot_dim; i += 32) dst[kv_rank + i] = r[i];
 }
 
+// One thread per rotary pair (or per copied element) of one (token, head): the work is spread over the whole grid
+// whatever the number of tokens.
 template <typename T>
-__global__ void __launch_bounds__(128) rope_heads_kernel(T* __restrict__ dst, int64_t dst_stride, int dst_head_stride,
+__global__ void __launch_bounds__(256) rope_heads_kernel(T* __restrict__ dst, int64_t dst_stride, int dst_head_stride,
                                                          const T* __restrict__ src, int64_t src_stride,
                                                          int src_head_stride, const float* __restrict__ cs_table,
                                                          int64_t tokens, int heads, int width, int rot_dims) {
   pdl_prologue();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t t = (int64_t)blockIdx.x * 4 + warp;
-  if (t >= tokens) return;
-  const int half = rot_dims / 2;
-  const float* cs = cs_table + t * rot_dims;
-  const T* s = src + t * src_stride;
-  T* d = dst + t * dst_stride;
-  for (int i = lane; i < heads * width; i += 32) {
-    const int h = i / width, c = i - h * width;
-    const T* sh = s + (int64_t)h * src_head_stride;
-    float v;
-    if (c < half) v = to_f32(sh[c]) * cs[c] - to_f32(sh[c + half]) * cs[half + c];
-    else if (c < 2 * half) v = to_f32(sh[c]) * cs[c - half] + to_f32(sh[c - half]) * cs[c];
-    else v = to_f32(sh[c]);
-    d[(int64_t)h * dst_head_stride + c] = from_f32<T>(v);
+  const int half = rot_dims / 2, per = width - half;            // items per (token, head): pairs, then the copied tail
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= tokens * heads * per) return;
+  const int64_t th = idx / per;
+  const int j = (int)(idx - th * per);
+  const int64_t t = th / heads;
+  const int h = (int)(th - t * heads);
+  const T* sh = src + t * src_stride + (int64_t)h * src_head_stride;
+  T* dh = dst + t * dst_stride + (int64_t)h * dst_head_stride;
+  if (j < half) {
+    const float c = cs_table[t * rot_dims + j], s = cs_table[t * rot_dims + half + j];
+    const float u = to_f32(sh[j]), v = to_f32(sh[j + half]);
+    dh[j] = from_f32<T>(u * c - v * s);
+    dh[j + half] = from_f32<T>(v * c + u * s);
+  } else {
+    dh[j + half] = sh[j + half];
   }
 }
 
@@ -143,7 +146,8 @@ extern "C" int b2l_rope_heads(void* dst, int64_t dst_row_stride, int dst_head_st
   if (tokens <= 0 || width == 0) return B2L_OK;
   cudaStream_t st = (cudaStream_t)stream;
   B2L_DISPATCH_FLOAT(dtype, "rope_heads", {
-    b2l_launch(rope_heads_kernel<T>, dim3((unsigned)cdiv64(tokens, 4)), dim3(128), (size_t)0, st, (T*)dst, dst_row_stride,
+    b2l_launch(rope_heads_kernel<T>, dim3((unsigned)cdiv64(tokens * heads * (width - rot_dims / 2), 256)), dim3(256),
+               (size_t)0, st, (T*)dst, dst_row_stride,
                dst_head_stride, (const T*)src, src_row_stride, src_head_stride, (const float*)cos_sin_f32, tokens, heads,
                width, rot_dims);
   });

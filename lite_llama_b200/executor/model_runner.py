@@ -239,12 +239,13 @@ class RequestState:
     """What the runner keeps per live request of a ragged-step model: its slot (row of the request table and
     recurrent-state slot), how many tokens it has in the cache / state, and the pool rows it holds."""
 
-    __slots__ = ("slot", "num_cached", "rows")
+    __slots__ = ("slot", "num_cached", "rows", "released")
 
     def __init__(self, slot: int) -> None:
         self.slot = slot
         self.num_cached = 0
-        self.rows: list[int] = []
+        self.rows: list[int] = []          # the pool row of every position so far (released ones keep their entry)
+        self.released = 0                  # positions [0, released) have given their rows back (sliding windows)
 
 
 class ModelRunner:
@@ -297,6 +298,11 @@ class ModelRunner:
         self.kv_cache_manager = KVCacheManager(len(attn), 0, 0, max_tokens, dtype=self.dtype, device=self.device,
                                                row_widths=widths)
         self.kv_buffer_of = dict(zip(attn, self.kv_cache_manager.gpu_kv_buffer))
+        # when EVERY cached layer has a sliding window, positions that no later token can see give their rows back
+        # while the request is still running: the longest window, plus one 64-key attention tile of slack (the tiled
+        # kernel starts its first key tile on a tile boundary below the window)
+        windows = [getattr(config.layers[i].mixer, "window", 0) for i in attn]
+        self.keep_positions = max(windows) - 1 + 64 if windows and min(windows) > 0 else 0
         self.state_manager = RecurrentStateManager(config, max_requests, self.dtype, self.device)
         self.b_req_tokens_table = torch.zeros((max_requests, self.max_seq_len), dtype=torch.int32, device=self.device)
         self.atten_info = AttentionMetadata(kv_buffer=self.kv_cache_manager.gpu_kv_buffer,
@@ -346,10 +352,22 @@ class ModelRunner:
     def close_request(self, req: RequestState) -> None:
         """Give the request's pool rows and its slot back."""
         if req.rows:
-            self.kv_cache_manager.release_rows_host(req.rows)
+            self.kv_cache_manager.release_rows_host(req.rows[req.released:])
             req.rows = []
         self.state_manager.release(req.slot)
-        req.num_cached = 0
+        req.num_cached = req.released = 0
+
+    def _release_unseen_rows(self, req: RequestState) -> None:
+        """Sliding windows: the next token (position ``num_cached``) and all later ones see no position below
+        ``num_cached - keep_positions``; those rows go back to the pool now."""
+        if self.keep_positions:
+            dead = req.num_cached - self.keep_positions
+            if dead > req.released:
+                self.kv_cache_manager.release_rows_host(req.rows[req.released:dead])
+                req.released = dead
+
+    def rows_held(self, req: RequestState) -> int:
+        return len(req.rows) - req.released
 
     def rows_needed(self, tokens: int) -> int:
         return tokens
@@ -398,6 +416,7 @@ class ModelRunner:
                 logits = self._ragged_graphs[(total, cap)].replay(host.pin_memory())
                 for req, _ in entries:
                     req.num_cached += 1
+                    self._release_unseen_rows(req)
                 return logits
         host = torch.tensor(flat_ids + table_idx + rows + list(want), dtype=torch.int32)
         dev = (host.pin_memory() if torch.cuda.is_available() else host).to(self.device, non_blocking=True)
@@ -408,6 +427,7 @@ class ModelRunner:
                                     want_rows)
         for (req, _), n in zip(entries, lens):
             req.num_cached += n
+            self._release_unseen_rows(req)
         return logits
 
     # ------------------------------------------------------------------ build #

@@ -411,6 +411,44 @@ def test_long_decoding_carries_the_window_over_decoded_tokens_and_key_range_edge
     _close(got, ref, 1e-4)
 
 
+def test_rows_outside_every_window_return_to_the_pool_while_the_request_runs():
+    """Every layer has a window, so a running request holds only the rows a later token can still see (the longest
+    window and one key tile of slack): two sequences of 400 and 300 tokens run side by side through a pool of 256 rows,
+    in portions and token by token, and every logit equals the restatement."""
+    a = O.mixer_entry(heads=2, dim=8, rot_dim=4, vdim=8, q_rank=8, kv_rank=12, window=33)
+    b = O.mixer_entry(heads=2, dim=8, rot_dim=4, vdim=8, q_rank=8, kv_rank=4, window=20)
+    cfg = O.make_config([O.layer_entry(a, None), O.layer_entry(b, O.moe_entry(experts=4, top=2, groups=2, keep=1, ff=8,
+                                                                            shared_ff=0))], width=16, vocab=40)
+    w = O.random_model(cfg, seed=17)
+    toks = [_tokens(cfg, 400, 5), _tokens(cfg, 300, 6)]
+    refs = [O.forward(cfg, w, t) for t in toks]
+    runner = _runner(cfg, w, max_tokens=256, max_requests=2)
+    assert runner.keep_positions == 32 + 64
+    reqs = [runner.open_request(), runner.open_request()]
+    plans = [[20, 3, 17, 2] * 4 + [1] * 400, [1, 30, 1, 9] * 5 + [1] * 300]
+    fed, got = [0, 0], [[], []]
+    while fed[0] < 400 or fed[1] < 300:
+        entries, want, at, shape = [], [], 0, []
+        for i in (0, 1):
+            if fed[i] < len(toks[i]):
+                n = min(plans[i].pop(0), len(toks[i]) - fed[i])
+                entries.append((reqs[i], toks[i][fed[i]:fed[i] + n]))
+                want += list(range(at, at + n))
+                at += n
+                shape.append((i, n))
+        logits = runner.forward_ragged(entries, want)
+        at = 0
+        for i, n in shape:
+            got[i].append(logits[at:at + n])
+            at += n
+            fed[i] += n
+            assert runner.rows_held(reqs[i]) <= 96 + n
+    for i in (0, 1):
+        _close(torch.cat(got[i]), refs[i], 1e-4)
+        runner.close_request(reqs[i])
+    assert runner.kv_cache_manager.can_use_mem_size == 256
+
+
 def test_a_far_key_outside_the_window_is_forgotten_and_one_inside_is_found():
     """The model as a whole: changing a token that lies outside every layer's reach leaves the logits of the last
     position untouched, changing one inside the first layer's window does not."""

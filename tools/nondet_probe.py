@@ -23,7 +23,7 @@ pk = K.w4a16_pack(qw, sc, zp, group_size=128)
 if a.flags:
     import ctypes
     from lite_llama_b200 import _lib
-    L = _lib.load(); L.b2l_debug_set_flags.argtypes = [ctypes.c_int]; L.b2l_debug_set_flags.restype = ctypes.c_int
+    L = _lib.load().cdll; L.b2l_debug_set_flags.argtypes = [ctypes.c_int]; L.b2l_debug_set_flags.restype = ctypes.c_int
     L.b2l_debug_set_flags(a.flags)
 outs = []
 for _ in range(a.reps):

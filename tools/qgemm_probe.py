@@ -28,7 +28,7 @@ def main():
     ap.add_argument("--shapes", default="qkv,o,gate_up,down")
     ap.add_argument("--flags", default="base,no_streamk,pair_k4,raw_operand,no_streamk+pair_k4,no_streamk+raw")
     a = ap.parse_args()
-    lib = _lib.load()
+    lib = _lib.load().cdll          # debug symbols are not part of the declared ABI
     lib.b2l_debug_set_flags.argtypes = [ctypes.c_int]
     lib.b2l_debug_set_flags.restype = ctypes.c_int
     dev = "cuda"

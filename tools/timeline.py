@@ -26,7 +26,7 @@ def main():
     ap.add_argument("--brief", action="store_true")
     ap.add_argument("--packed", action="store_true", help="kernel-native W4A16 layout (w4a16_pack)")
     a = ap.parse_args()
-    lib = _lib.load()
+    lib = _lib.load().cdll          # debug symbols are not part of the declared ABI
     lib.b2l_debug_set_timeline.argtypes = [ctypes.c_void_p]
     lib.b2l_debug_set_timeline.restype = ctypes.c_int
     lib.b2l_debug_set_flags.argtypes = [ctypes.c_int]

@@ -29,7 +29,7 @@ def main():
     ap.add_argument("--m", type=int, default=32)
     ap.add_argument("--chain", type=int, default=6)
     a = ap.parse_args()
-    lib = _lib.load()
+    lib = _lib.load().cdll          # debug symbols are not part of the declared ABI
     lib.b2l_debug_set_timeline.argtypes = [ctypes.c_void_p]
     lib.b2l_debug_set_timeline.restype = ctypes.c_int
     dev = "cuda"
