@@ -75,12 +75,18 @@ class Engine:
             raise ValueError("a request needs a non-empty prompt and at least one new token")
         if len(prompt) + max_new_tokens > self.runner.max_seq_len:
             raise ValueError(f"prompt + new tokens exceed max_seq_len {self.runner.max_seq_len}")
-        if self._pool is not None and len(prompt) + max_new_tokens > self._pool:
+        if self._pool is not None and self._rows(len(prompt) + max_new_tokens) > self._pool:
             raise ValueError("the request alone exceeds the KV pool")
         rid = self._next_id
         self._next_id += 1
         self.waiting.append(GenerationRequest(rid, prompt, max_new_tokens, eos_token_id))
         return rid
+
+    def _rows(self, tokens: int) -> int:
+        """Pool rows a sequence of ``tokens`` holds at most: all of them, or -- when every cached layer has a sliding
+        window and the runner gives unseen rows back on the way -- what the windows keep plus one portion."""
+        keep = getattr(self.runner, "keep_positions", 0)
+        return min(tokens, keep + self.max_portion) if keep else tokens
 
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
@@ -88,11 +94,11 @@ class Engine:
     def _admit(self) -> None:
         while self.waiting and self._slots_free > 0:
             req = self.waiting[0]
-            if self._pool is not None and self._reserved + req.reserve > self._pool:
+            if self._pool is not None and self._reserved + self._rows(req.reserve) > self._pool:
                 break
             self.waiting.popleft()
             self._slots_free -= 1
-            self._reserved += req.reserve
+            self._reserved += self._rows(req.reserve)
             if self.runner.ragged_steps:
                 req.state = self.runner.open_request()
             else:
@@ -107,7 +113,7 @@ class Engine:
         else:
             self._free_slots.append(req.slot)
         self._slots_free += 1
-        self._reserved -= req.reserve
+        self._reserved -= self._rows(req.reserve)
         self.running.remove(req)
         self.done[req.rid] = req
 

@@ -250,7 +250,8 @@ class RequestState:
 
 class ModelRunner:
     def __init__(self, config: ModelConfig | LayeredConfig, weights, max_gpu_num_blocks: int,
-                 device: str = "cuda", dtype: torch.dtype = torch.float16, max_requests: int | None = None) -> None:
+                 device: str = "cuda", dtype: torch.dtype = torch.float16, max_requests: int | None = None,
+                 max_seq_len: int | None = None) -> None:
         self.config = config
         self.device = device
         self.dtype = dtype
@@ -261,7 +262,7 @@ class ModelRunner:
         self._graph_buckets: tuple[int, ...] = ()
         self._ragged_graphs: dict[tuple[int, int], _CapturedRaggedDecode] = {}
         if self.ragged_steps:
-            self._init_layered(config, weights, max_gpu_num_blocks, max_requests or 4)
+            self._init_layered(config, weights, max_gpu_num_blocks, max_requests or 4, max_seq_len)
             return
         self.num_layers = config.num_layers
         self.num_kv_heads = divide(config.num_kv_heads, get_tp_world_size(), "key/value heads")
@@ -283,15 +284,14 @@ class ModelRunner:
         counters(torch.device(device))  # allocate the split-K ticket buffer outside any capture
 
     # ------------------------------------------------------- layer-list models #
-    def _init_layered(self, config: LayeredConfig, weights, max_tokens: int, max_requests: int) -> None:
+    def _init_layered(self, config: LayeredConfig, weights, max_tokens: int, max_requests: int,
+                      max_seq_len: int | None = None) -> None:
         """Pool of ``max_tokens`` rows shared by all requests (one 2-D buffer per attention layer: layers may differ
         in head count and K / V head size), ``max_requests`` slots of recurrent state, one request -> rows table."""
         from .layered_decoder import LayeredDecoder
 
         self.num_layers = config.num_layers
         self.vocab_size = config.vocab_size
-        # a design without a position table takes sequences as long as the pool
-        self.max_seq_len = config.max_seq_len if config.max_seq_len > 0 else max_tokens
         self.max_request_num = max_requests
         attn = config.attention_layers()
         widths = [config.layers[i].mixer.cache_row_width for i in attn]
@@ -303,6 +303,14 @@ class ModelRunner:
         # kernel starts its first key tile on a tile boundary below the window)
         windows = [getattr(config.layers[i].mixer, "window", 0) for i in attn]
         self.keep_positions = max(windows) - 1 + 64 if windows and min(windows) > 0 else 0
+        # longest sequence = columns of the request table: the position table's length; without one, the pool's size, or
+        # (rows are given back on the way) as far as the caller asks, 64k positions by default
+        if config.max_seq_len > 0:
+            self.max_seq_len = config.max_seq_len
+        elif max_seq_len:
+            self.max_seq_len = max_seq_len
+        else:
+            self.max_seq_len = max(max_tokens, 65536) if self.keep_positions else max_tokens
         self.state_manager = RecurrentStateManager(config, max_requests, self.dtype, self.device)
         self.b_req_tokens_table = torch.zeros((max_requests, self.max_seq_len), dtype=torch.int32, device=self.device)
         self.atten_info = AttentionMetadata(kv_buffer=self.kv_cache_manager.gpu_kv_buffer,
