@@ -298,7 +298,7 @@ int b2l_moe_gemm_simt(void* c, const void* a, const void* w, const void* slot_we
                       int64_t c_row_stride, int act, int dtype, void* stream);
 /* Tensor-core (mma.sync, fp32 accumulators) versions of b2l_head_linear and b2l_moe_gemm_simt for 16-bit dtypes
  * (csrc/gemm_rows_mma.cu); b2l_rows_gemm_mma_ok says whether they take the operands (k and the x strides multiples
- * of 8 elements, 16-byte aligned bases).  b2l_moe_gemm_mma: block_size 16 or 64 = the block size of the alignment. */
+ * of 8 elements, 16-byte aligned bases).  b2l_moe_gemm_mma: block_size 16, 64 or 128 = the block size of the alignment. */
 int b2l_rows_gemm_mma_ok(const void* x, const void* w, int64_t k, int64_t x_row_stride, int64_t x_head_stride,
                          int dtype);
 int b2l_head_linear_mma(void* y, int64_t y_row_stride, int64_t y_head_stride, const void* x, int64_t x_row_stride,

@@ -230,11 +230,12 @@ def grouped_experts(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, w
     mid = torch.empty((slots, ff), dtype=x.dtype, device=x.device)
     expanded = torch.empty((slots, hidden), dtype=x.dtype, device=x.device)
     flat_w = weights.reshape(-1).contiguous()
-    # 16-bit operands with 16-byte aligned rows run on the tensor cores (64-slot blocks, 16 when an expert sees few
-    # slots), everything else on the CUDA cores; the result of a slot does not depend on the block size
+    # 16-bit operands with 16-byte aligned rows run on the tensor cores (blocks of 16, 64 or 128 slots by the expected
+    # slots per expert), everything else on the CUDA cores; the result of a slot does not depend on the block size
     tensor = bool(L.b2l_rows_gemm_mma_ok(x.data_ptr(), w_up.data_ptr(), hidden, x.stride(0), 0, code)) and \
         bool(L.b2l_rows_gemm_mma_ok(mid.data_ptr(), w_down.data_ptr(), ff, mid.stride(0), 0, code))
-    block = (64 if slots > 16 * num_experts else 16) if tensor else L.b2l_moe_gemm_simt_block()
+    per_expert = slots / num_experts
+    block = (16 if per_expert <= 16 else (64 if per_expert <= 256 else 128)) if tensor else L.b2l_moe_gemm_simt_block()
     sorted_ids, expert_ids, num_post = moe_align_block_size(ids, block, num_experts)
     common = (sorted_ids.data_ptr(), expert_ids.data_ptr(), num_post.data_ptr(), sorted_ids.numel(), slots)
     if tensor:
