@@ -269,13 +269,13 @@ P_SIZES = {
 def pesivik_config(sz: dict) -> dict:
     layer = {"type": "latent_attention",
              "mixer": {"dim": sz["dim"], "heads": sz["heads"], "kv_rank": sz["kv_rank"], "mask": {"size": sz["window"]},
-                       "q_rank": sz["q_rank"], "rot": {"base": 500000.0, "dims": sz["rot_dim"]}, "rot_dim": sz["rot_dim"],
+                       "q_rank": sz["q_rank"], "rot": {"base": 1.0e6, "dims": sz["rot_dim"]}, "rot_dim": sz["rot_dim"],
                        "scale": 1.0 / math.sqrt(sz["dim"] + sz["rot_dim"]), "vdim": sz["vdim"]},
              "mlp": {"expert": {"ff": sz["ff"]}, "kind": "moe", "shared": {"ff": sz["shared_ff"]},
                      "router": {"experts": sz["experts"], "top": sz["top"],
                                 "groups": {"count": sz["groups"], "keep": sz["keep"]}}}}
     return {"architecture": "Pesivik", "embedding": {"scale": 1.0}, "layers": [dict(layer) for _ in range(sz["layers"])],
-            "logit_softcap": 30.0, "norm": {"eps": 1e-5}, "vocab": sz["vocab"], "width": sz["width"]}
+            "logit_softcap": 50.0, "norm": {"eps": 1e-6}, "vocab": sz["vocab"], "width": sz["width"]}
 
 
 def build_pesivik(sz, batch, max_positions, dev, dtype):
@@ -424,8 +424,8 @@ def pesivik_kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) 
     rows_p = table[:, :ctx].reshape(-1).contiguous()
     pos_p = i32(list(range(prompt)) * batch)
     wq, wkv = rnd(qr, s=0.1) + 1, rnd(kr, s=0.1) + 1
-    cs = K.rope_table(pos_p, rot, 500000.0)
-    add("rope_table (once per step)", None, lambda: K.rope_table(pos_p, rot, 500000.0), nbytes=T * (4 + rot * 4))
+    cs = K.rope_table(pos_p, rot, 1.0e6)
+    add("rope_table (once per step)", None, lambda: K.rope_table(pos_p, rot, 1.0e6), nbytes=T * (4 + rot * 4))
     upool = rnd(batch * (ctx + 1), 2 * G * UD, dt=f16, s=0.5)
     uqkv = rnd(T, (H + 2 * G) * UD, dt=f16, s=0.5)
     cos = rnd(batch, prompt, UD, dt=f16)
@@ -500,7 +500,7 @@ def pesivik_kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) 
         nbytes=active * 2 * ff * W * es, like_fn=lambda: K.fused_moe(xd16, w1, w2, twd, tidd),
         like_bytes=active_u * 3 * ff * W * es)
     logits = rnd(batch, sz["vocab"], s=8.0)
-    add("softcap_to_f32 (logits)", None, lambda: K.softcap_to_f32(logits, 30.0), nbytes=batch * sz["vocab"] * (es + 4))
+    add("softcap_to_f32 (logits)", None, lambda: K.softcap_to_f32(logits, 50.0), nbytes=batch * sz["vocab"] * (es + 4))
     return rows
 
 

@@ -191,7 +191,7 @@ def test_windowed_attention_on_the_latent_rows(dtype, tol, heads, rank, rot, win
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("window,ctx", [(40, 100), (64, 64), (65, 300), (129, 400)])
+@pytest.mark.parametrize("window,ctx", [(37, 100), (64, 64), (65, 300), (129, 400)])
 def test_the_key_at_the_window_edge_counts_and_the_next_one_does_not(dtype, window, ctx):
     """One key is made to dominate its query's scores.  Just inside the window (distance window - 1) the output is
     that key's latent; one step further out it must have no influence at all -- for a token inside a portion and for
@@ -207,7 +207,7 @@ def test_the_key_at_the_window_edge_counts_and_the_next_one_does_not(dtype, wind
         assert (ref_in[row] - ref_out[row]).abs().max() > 0.5          # the case does tell the two apart
 
 
-@pytest.mark.parametrize("experts,top,groups,keep", [(8, 3, 4, 2), (12, 3, 3, 2), (6, 1, 6, 1), (5, 2, 1, 1), (64, 8, 8, 4),
+@pytest.mark.parametrize("experts,top,groups,keep", [(8, 3, 4, 2), (15, 4, 5, 3), (6, 1, 6, 1), (5, 2, 1, 1), (64, 8, 8, 4),
                                                      (4, 4, 2, 2), (40, 34, 2, 2)])
 def test_router_with_selection_bias_and_group_limit(experts, top, groups, keep):
     from lite_llama_b200.kernels import route_sigmoid_groups
@@ -266,15 +266,15 @@ def _small():
 def _aligned(every_expert=False):
     # sizes in steps of 8: the tensor-core attention tiles in bf16; a window longer than a 64-key tile; the later
     # layer is the one that owns the weights
-    a = O.mixer_entry(heads=4, dim=16, rot_dim=8, vdim=24, q_rank=40, kv_rank=24, window=70, base=500000.0)
+    a = O.mixer_entry(heads=4, dim=16, rot_dim=8, vdim=24, q_rank=40, kv_rank=24, window=70, base=1.0e6)
     b = O.mixer_entry(heads=2, dim=32, rot_dim=16, vdim=16, q_rank=32, kv_rank=48, window=16)
-    big = O.moe_entry(experts=12, top=3, groups=3, keep=2, ff=24, shared_ff=32)
+    big = O.moe_entry(experts=15, top=4, groups=5, keep=3, ff=24, shared_ff=32)
     little = O.moe_entry(experts=4, top=2, groups=2, keep=1, ff=16, shared_ff=8)
     if every_expert:                                        # top == experts: the router only weighs
         big = O.moe_entry(experts=3, top=3, groups=1, keep=1, ff=24, shared_ff=32)
         little = O.moe_entry(experts=2, top=2, groups=2, keep=2, ff=16, shared_ff=8)
     return O.make_config([O.layer_entry(a, big, 2), O.layer_entry(b, little), O.layer_entry(a, big)],
-                         width=64, vocab=128, softcap=30.0)
+                         width=64, vocab=128, softcap=25.0)
 
 
 def _ones():
