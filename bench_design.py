@@ -478,6 +478,23 @@ def pesivik_kernel_table(sz, batch, prompt, dev, dtype, flush, hbm_gbs, tflops) 
         like_fn=lambda: K.flash_decoding(q3[:batch], upool.view(-1, 2 * G, UD)[:, :G], upool.view(-1, 2 * G, UD)[:, G:], scale,
                                          table, p_slot, seq1, ctx + 1),
         like_bytes=batch * (ctx + 1) * 2 * G * UD * es)
+    # the same at a long context without a window: 8 sequences x 8193 keys
+    lctx = 8192
+    lpool = rnd(batch * (lctx + 1), D, s=0.5)
+    ltable = torch.arange(batch * (lctx + 1), dtype=torch.int32, device=dev).view(batch, lctx + 1)
+    l_ctx = i32([lctx] * batch)
+    lsplits = max(1, min(128, -(-(lctx + 1) // 128)))
+    lper = -(-(-(-(lctx + 1) // lsplits)) // 32) * 32
+    lupool = rnd(batch * (lctx + 1), 2 * G * UD, dt=f16, s=0.5)
+    lseq = torch.full((batch,), lctx + 1, dtype=torch.int32, device=dev)
+    add("attention over latent rows (decode, %d keys, no window)" % (lctx + 1), "flash_decoding (context %d)" % (lctx + 1),
+        lambda: K.sink_attention(lat, qa, lpool, ltable, d_start, l_ctx, p_slot, None, batch, 1, None, H, 1, D, kr, scale, 0.0,
+                                 num_splits=lsplits, split_keys=lper, window=0, v_col0=0),
+        nbytes=batch * (lctx + 1) * D * es,
+        like_fn=lambda: K.flash_decoding(q3[:batch], lupool.view(-1, 2 * G, UD)[:, :G], lupool.view(-1, 2 * G, UD)[:, G:], scale,
+                                         ltable, p_slot, lseq, lctx + 1),
+        like_bytes=batch * (lctx + 1) * 2 * G * UD * es)
+    del lpool, lupool
     # ---------------- router and experts
     x = rnd(T, W, s=0.5)
     rw, rb = rnd(E, W, s=0.05), rnd(E, s=0.1)

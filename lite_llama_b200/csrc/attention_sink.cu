@@ -15,7 +15,10 @@
 //                    sequence) on the CUDA cores; the rows of a CTA (tokens x the kv head's query heads) share every
 //                    K/V tile that is staged in shared memory
 //                  * split mode (one new token per sequence: decode): CTA = (key range, kv head, sequence), fp32
-//                    partial (max, sum, acc) per range, merged with the sink by sink_attention_merge
+//                    partial (max, sum, acc) per range, merged with the sink by sink_attention_merge.  With more than 4
+//                    query heads per kv head (a latent cache: ALL heads share one row) and 16-bit T the partials come
+//                    from the tensor-core kernel with the HEADS as the rows of its tile: a cached row is read once
+//                    per key range and scored against every head by mma
 // Softmax statistics, scores and the output accumulator are fp32 whatever T is.
 #include "common.cuh"
 
@@ -36,6 +39,8 @@ struct AttnArgs {
   float* part;
   int H, G, D, Dv, PH, BQ, nsplit, chunk;
   int window, v_col0;          // window <= 0: every earlier key is visible; v_col0: first value column of a pool row
+  int head_rows;               // tensor-core kernel, one new token per sequence: the tile's rows are the query HEADS of
+                               // one kv head (not tokens), blockIdx.x is a key range, results go to `part`
   float scale, softcap;
 };
 
@@ -187,27 +192,38 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(AttnArgs a) {
   const int D = a.D, Dv = a.Dv, per = a.H / a.G;
   const int z = blockIdx.z, s = a.seq_list ? a.seq_list[z] : z;
   const int start = a.seq_start[s], qlen = a.seq_start[s + 1] - start, ctx = a.seq_ctx[s];
-  const int t0 = blockIdx.x * kTileM;
-  if (t0 >= qlen) return;
-  const int t_count = min(kTileM, qlen - t0);
-  const int h = blockIdx.y, g = h / per;
-  const int64_t slot = a.seq_slot[s];
-  const int key_hi = ctx + t0 + t_count;                         // exclusive
+  const bool hr = a.head_rows != 0;
+  const int t0 = hr ? 0 : blockIdx.x * kTileM;
+  if (!hr && t0 >= qlen) return;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int gq = lane >> 2, tq = lane & 3;
   const int r0 = warp * 16 + gq, r1 = r0 + 8;                    // rows of the tile
+  // token rows: row r = token t0 + r of head blockIdx.y.  head rows: row r = head h_base + r of the ONE new token,
+  // blockIdx.y = (kv head, 64-head chunk of its query heads), blockIdx.x = key range
+  const int hchunks = (per + kTileM - 1) / kTileM;
+  const int g = hr ? blockIdx.y / hchunks : blockIdx.y / per;
+  const int h_base = hr ? g * per + (blockIdx.y % hchunks) * kTileM : blockIdx.y;
+  const int t_count = hr ? min(kTileM, g * per + per - h_base) : min(kTileM, qlen - t0);       // live rows
+  const int h = h_base;
+  const int64_t slot = a.seq_slot[s];
+  const int win_lo = a.window > 0 ? max(0, ctx - a.window + 1) : 0;            // head rows: the token's first visible key
+  const int range_lo = hr ? win_lo + blockIdx.x * a.chunk : 0;
+  const int key_hi = hr ? min(range_lo + a.chunk, ctx + 1) : ctx + t0 + t_count;               // exclusive
   const bool ok0 = r0 < t_count, ok1 = r1 < t_count;
-  const int pos0 = ctx + t0 + r0, pos1 = ctx + t0 + r1;          // last visible key of each row
-  const int lo0 = a.window > 0 ? pos0 - a.window + 1 : 0, lo1 = a.window > 0 ? pos1 - a.window + 1 : 0;   // first one
-  // first key tile: the one that holds the first key of the tile's first token (tiles stay aligned to kTileN)
-  const int k_first = a.window > 0 ? max(0, ctx + t0 - a.window + 1) / kTileN * kTileN : 0;
-  const int warp_first = a.window > 0 ? ctx + t0 + warp * 16 - a.window + 1 : 0;      // first key of the warp's rows
+  const int pos0 = hr ? key_hi - 1 : ctx + t0 + r0, pos1 = hr ? key_hi - 1 : ctx + t0 + r1;     // last visible key of each row
+  const int lo0 = hr ? range_lo : (a.window > 0 ? pos0 - a.window + 1 : 0);                     // first one
+  const int lo1 = hr ? range_lo : (a.window > 0 ? pos1 - a.window + 1 : 0);
+  // first key tile: the one that holds the first key of the tile's first row (tiles stay aligned to kTileN)
+  const int k_first = hr ? range_lo / kTileN * kTileN : (a.window > 0 ? max(0, ctx + t0 - a.window + 1) / kTileN * kTileN : 0);
+  const int warp_first = hr ? range_lo : (a.window > 0 ? ctx + t0 + warp * 16 - a.window + 1 : 0);   // first key of the warp's rows
   const T* q = (const T*)a.q;
   const T* kv = (const T*)a.kv;
   uint32_t qf[DP / 16][4];
   {
-    const T* q0 = q + (int64_t)(start + t0 + (ok0 ? r0 : 0)) * a.q_stride + h * D;
-    const T* q1 = q + (int64_t)(start + t0 + (ok1 ? r1 : 0)) * a.q_stride + h * D;
+    const T* q0 = hr ? q + (int64_t)start * a.q_stride + (h_base + (ok0 ? r0 : 0)) * D
+                     : q + (int64_t)(start + t0 + (ok0 ? r0 : 0)) * a.q_stride + h * D;
+    const T* q1 = hr ? q + (int64_t)start * a.q_stride + (h_base + (ok1 ? r1 : 0)) * D
+                     : q + (int64_t)(start + t0 + (ok1 ? r1 : 0)) * a.q_stride + h * D;
 #pragma unroll
     for (int kk = 0; kk < DP / 16; ++kk) {
       const int c = kk * 16 + 2 * tq;
@@ -221,7 +237,8 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(AttnArgs a) {
 #pragma unroll
   for (int i = 0; i < DVP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  const int warp_last = ctx + t0 + warp * 16 + 15;
+  // last key any row of the warp sees; a warp without live rows (head rows: fewer than 16 * warp heads) sees none
+  const int warp_last = hr ? (warp * 16 < t_count ? key_hi - 1 : -1) : ctx + t0 + warp * 16 + 15;
   const int* trow = a.table + slot * a.table_stride;
   const float cap = a.softcap, inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
   // tile k0 -> stage `st`: asynchronous 16-byte copies of the rows the table names; rows / columns past the end are
@@ -260,7 +277,7 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(AttnArgs a) {
     }
     cp_async_commit();
   };
-  issue(k_first, 0);
+  if (k_first < key_hi) issue(k_first, 0);
   for (int k0 = k_first, it = 0; k0 < key_hi; k0 += kTileN, ++it) {
     const bool more = k0 + kTileN < key_hi;
     if (more) issue(k0 + kTileN, (it + 1) & 1);                  // the next tile flies while this one is used
@@ -348,6 +365,25 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(AttnArgs a) {
     }
     __syncthreads();
   }
+  if (hr) {
+    // one fp32 partial (max, sum, unnormalised values) per (head, key range) in the layout sink_attention_merge reads;
+    // the maximum goes back from the log2 domain to natural units
+#pragma unroll
+    for (int r2 = 0; r2 < 2; ++r2) {
+      l_run[r2] += __shfl_xor_sync(0xffffffffu, l_run[r2], 1);
+      l_run[r2] += __shfl_xor_sync(0xffffffffu, l_run[r2], 2);
+      const int r = r2 ? r1 : r0;
+      if (r >= t_count) continue;
+      float* dst = a.part + (((int64_t)z * a.H + h_base + r) * a.nsplit + blockIdx.x) * (Dv + 2);
+      if (tq == 0) { dst[0] = m_run[r2] * 0.6931471805599453f; dst[1] = l_run[r2]; }
+#pragma unroll
+      for (int i = 0; i < DVP / 8; ++i) {
+        const int c = i * 8 + 2 * tq;
+        if (c < Dv) { dst[2 + c] = o[i][2 * r2]; dst[3 + c] = o[i][2 * r2 + 1]; }
+      }
+    }
+    return;
+  }
   float inv[2];
 #pragma unroll
   for (int r2 = 0; r2 < 2; ++r2) {
@@ -382,7 +418,9 @@ int launch_attention_mma(const AttnArgs& a, int max_q_len, int64_t num_seqs, cud
   constexpr int smem = 2 * kTileN * ((DP + 8) * 2 + (DVP + 8) * 2);      // two stages
   static int cache[64] = {0};
   B2L_CUDA_CHECK(b2l_ensure_dynamic_smem(sink_attention_mma_kernel<T, DP, DVP>, smem, cache));
-  const dim3 grid((unsigned)((max_q_len + kTileM - 1) / kTileM), (unsigned)a.H, (unsigned)num_seqs);
+  const int per = a.H / a.G;
+  const dim3 grid = a.head_rows ? dim3((unsigned)a.nsplit, (unsigned)(a.G * ((per + kTileM - 1) / kTileM)), (unsigned)num_seqs)
+                                : dim3((unsigned)((max_q_len + kTileM - 1) / kTileM), (unsigned)a.H, (unsigned)num_seqs);
   b2l_launch(sink_attention_mma_kernel<T, DP, DVP>, grid, dim3(128), (size_t)smem, st, a);
   B2L_LAUNCH_CHECK();
   return B2L_OK;
@@ -861,6 +899,7 @@ extern "C" int b2l_sink_attention(void* out, int64_t out_row_stride, const void*
   a.nsplit = num_splits; a.chunk = split_keys; a.scale = scale; a.softcap = softcap;
   a.window = window > 0 ? window : 0;
   a.v_col0 = v_col0 >= 0 ? v_col0 : kv_heads * head_dim;
+  a.head_rows = 0;
   const int hchunks = (per + a.PH - 1) / a.PH;
   if (num_splits > 0) {
     B2L_REQUIRE(split_keys > 0, "sink_attention: split_keys must be positive");
@@ -868,7 +907,16 @@ extern "C" int b2l_sink_attention(void* out, int64_t out_row_stride, const void*
     B2L_REQUIRE(workspace && workspace_bytes >= need, "sink_attention: workspace too small (%lld < %lld)",
                 (long long)workspace_bytes, (long long)need);
     int rc = B2L_OK;
-    B2L_DISPATCH_FLOAT(dtype, "sink_attention", { rc = launch_attention_split<T>(a, num_seqs, st); });
+    // many query heads per kv head (latent caches: ALL heads share one row): the heads become the rows of a tensor-core
+    // tile, so a cached row is read once and scored against every head by mma instead of 4 heads at a time on the
+    // CUDA cores; same partials, same merge
+    if (per > kSplitRows && mma_path_ok(a, dtype)) {
+      a.head_rows = 1;
+      rc = dtype == B2L_F16 ? dispatch_attention_mma<__half>(a, 1, num_seqs, st)
+                            : dispatch_attention_mma<__nv_bfloat16>(a, 1, num_seqs, st);
+    } else {
+      B2L_DISPATCH_FLOAT(dtype, "sink_attention", { rc = launch_attention_split<T>(a, num_seqs, st); });
+    }
     if (rc != B2L_OK) return rc;
     B2L_DISPATCH_FLOAT(dtype, "sink_attention", {
       b2l_launch(sink_attention_merge_kernel<T>, dim3((unsigned)heads, (unsigned)num_seqs), dim3(64), (size_t)0, st,

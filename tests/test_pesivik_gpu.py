@@ -181,7 +181,7 @@ def _window_case(heads, rank, rot, seqs, window, dtype, boost=None, seed=0):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("heads,rank,rot,window", [(3, 12, 4, 7), (2, 24, 8, 70), (5, 10, 3, 1), (2, 16, 16, 150),
-                                                   (1, 40, 8, 0), (20, 8, 8, 33)])
+                                                   (1, 40, 8, 0), (20, 8, 8, 33), (70, 16, 8, 140), (6, 64, 16, 0)])
 def test_windowed_attention_on_the_latent_rows(dtype, tol, heads, rank, rot, window):
     """Portions with and without a cached prefix, single tokens, windows shorter and longer than a key tile (32 / 64)
     and than a key range of the single-token kernel (128); the values are the leading columns of the keys."""
@@ -191,17 +191,18 @@ def test_windowed_attention_on_the_latent_rows(dtype, tol, heads, rank, rot, win
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads", [2, 6])          # 6 heads on one cached row: single tokens take the heads-as-rows tiles
 @pytest.mark.parametrize("window,ctx", [(37, 100), (64, 64), (65, 300), (129, 400)])
-def test_the_key_at_the_window_edge_counts_and_the_next_one_does_not(dtype, window, ctx):
+def test_the_key_at_the_window_edge_counts_and_the_next_one_does_not(dtype, heads, window, ctx):
     """One key is made to dominate its query's scores.  Just inside the window (distance window - 1) the output is
     that key's latent; one step further out it must have no influence at all -- for a token inside a portion and for
     a token decoded alone."""
     rank, rot = 16, 8
     for new, t in ((12, 7), (1, 0)):                        # a portion's 8th token; a single token
         p = ctx + t
-        inside, ref_in = _window_case(2, rank, rot, [(3, 10), (new, ctx)], window, dtype, boost=(1, t, p - window + 1, 60.0))
+        inside, ref_in = _window_case(heads, rank, rot, [(3, 10), (new, ctx)], window, dtype, boost=(1, t, p - window + 1, 60.0))
         _close(inside, ref_in, 1e-5 if dtype == torch.float32 else 2e-2)
-        outside, ref_out = _window_case(2, rank, rot, [(3, 10), (new, ctx)], window, dtype, boost=(1, t, p - window, 60.0))
+        outside, ref_out = _window_case(heads, rank, rot, [(3, 10), (new, ctx)], window, dtype, boost=(1, t, p - window, 60.0))
         _close(outside, ref_out, 1e-5 if dtype == torch.float32 else 2e-2)
         row = 3 + t
         assert (ref_in[row] - ref_out[row]).abs().max() > 0.5          # the case does tell the two apart
