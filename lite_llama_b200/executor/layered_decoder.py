@@ -408,6 +408,15 @@ def parse_pesivik_config(raw: dict) -> LayeredConfig:
             raise ValueError(f"unknown feed-forward kind {mlp.get('kind')!r}")
         layers.append(LayerSpec(kind, mixer, _router_spec(mlp) if mlp is not None else None,
                                 weights_of=entry.get("weights_of")))
+    # a layer may name a layer that itself names another: every layer points at the one that owns the tensors
+    for i, spec in enumerate(layers):
+        j, hops = spec.weights_of, 0
+        while j is not None and 0 <= j < len(layers) and layers[j].weights_of is not None:
+            j, hops = layers[j].weights_of, hops + 1
+            if hops > len(layers):
+                raise ValueError(f"layer {i}: 'weights_of' runs in a circle")
+        if j != spec.weights_of:
+            layers[i] = LayerSpec(spec.kind, spec.mixer, spec.mlp, weights_of=j)
     return LayeredConfig(name=raw.get("architecture", "Pesivik"), hidden_size=int(raw["width"]),
                          vocab_size=int(raw["vocab"]), max_seq_len=0, rms_norm_eps=float(raw["norm"]["eps"]),
                          layers=tuple(layers), norm_kind="layer", pre_norm=True, layer_scale=True,

@@ -37,6 +37,20 @@ def test_config_parser_reads_every_size_and_constant():
     assert cfg.layers[1].mlp is None and cfg.layers[2].weights_of == 0 and cfg.layers[0].weights_of is None
 
 
+def test_a_chain_of_shared_layers_resolves_to_the_layer_that_owns_the_tensors():
+    from lite_llama_b200.executor.registry import lookup
+
+    a = O.mixer_entry()
+    raw = O.make_config([O.layer_entry(a, None, 2), O.layer_entry(a, None), O.layer_entry(a, None, 1), O.layer_entry(a, None, 0)])
+    cfg = lookup("Pesivik").parse_config(raw)
+    cfg.validate()
+    assert [l.weights_of for l in cfg.layers] == [1, None, 1, 1]
+    assert [O.source_layer(raw, i) for i in range(4)] == [1, 1, 1, 1]
+    raw["layers"][1]["weights_of"] = 3                         # a circle has no owner
+    with pytest.raises(ValueError):
+        lookup("Pesivik").parse_config(raw)
+
+
 def test_bad_configurations_are_refused():
     from lite_llama_b200.executor.registry import lookup
 
