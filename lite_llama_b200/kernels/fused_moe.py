@@ -211,8 +211,7 @@ def grouped_experts(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, w
     ``e = ids[t, k]``: ungated two-matrix experts, ``w_up [E, ff, h]``, ``w_down [E, h, ff]``.  Slots are sorted by
     expert (``moe_align_block_size``), both products run grouped (``mma.sync`` tiles for aligned 16-bit operands, the
     CUDA cores for true fp32 and odd shapes) with the activation in the first one's epilogue and the fp32 routing weight
-    in the second's.  The gated (SwiGLU) experts of
-    the reference's family are ``fused_moe``."""
+    in the second's.  The gated (SwiGLU) experts of the reference's family are ``fused_moe``."""
     require_cuda(x, w_up, w_down, weights, ids, addend)
     if activation != "gelu":
         raise ValueError(f"grouped_experts: unknown activation {activation!r}")

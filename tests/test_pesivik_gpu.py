@@ -8,6 +8,7 @@ spread; bf16 runs to a few bf16 roundings."""
 from __future__ import annotations
 
 import math
+import random
 
 import numpy as np
 import pytest
@@ -573,3 +574,88 @@ def test_engine_generates_past_the_pool_size_when_every_layer_has_a_window():
                 break
             assert t == int(logits.argmax())
             seq.append(t)
+
+
+# ------------------------------------------------------------------------------------- random models and schedules #
+def _random_config(rng, odd):
+    def mixer():
+        return O.mixer_entry(heads=rng.choice([1, 2, 3, 5, 6, 8]), dim=rng.choice([8, 12, 24, 32, 40, 64]),
+                             rot_dim=rng.choice([0, 2, 4, 8, 16, 32]), vdim=rng.choice([8, 10, 24, 40, 80]),
+                             q_rank=rng.choice([5, 30, 57] if odd else [8, 24, 56, 96]),
+                             kv_rank=rng.choice([4, 8, 20, 40, 64, 72, 128]),
+                             window=rng.choice([1, 2, 5, 16, 33, 64, 65, 100, 128, 200, 1000]),
+                             base=rng.choice([100.0, 10000.0, 1.0e6]))
+
+    def mlp():
+        if rng.random() < 0.2:
+            return None
+        groups, per = rng.choice([1, 2, 3, 4]), rng.choice([1, 2, 3, 4])
+        keep = rng.randint(1, groups)
+        return O.moe_entry(experts=groups * per, top=rng.randint(1, keep * per), groups=groups, keep=keep,
+                           ff=rng.choice([8, 12, 40, 96]), shared_ff=rng.choice([0, 16, 40]))
+
+    kinds = [(mixer(), mlp()) for _ in range(rng.randint(1, 2))]
+    layers, owner = [], {}
+    for i in range(rng.randint(2, 5)):
+        k = rng.randrange(len(kinds))
+        if k in owner and rng.random() < 0.7:
+            layers.append(O.layer_entry(kinds[k][0], kinds[k][1], owner[k]))
+        else:
+            layers.append(O.layer_entry(kinds[k][0], kinds[k][1]))
+            owner.setdefault(k, i)
+    return O.make_config(layers, width=rng.choice([50, 92, 37, 129] if odd else [16, 40, 72, 136, 200]),
+                         vocab=rng.choice([33, 1001] if odd else [17, 64, 300]), eps=rng.choice([1e-5, 1e-6, 1e-3]),
+                         embed_scale=rng.choice([0.5, 1.0, 2.0]), softcap=rng.choice([0.0, 10.0, 30.0]))
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_models_under_random_mixed_schedules(seed):
+    """Random sizes (odd widths, ranks and vocabularies on the odd seeds), layer orders with shared layers, windows from
+    1 to beyond the sequences; up to four requests fed in random portions beside one another through a pool of exactly
+    their size, the tails token by token.  fp32 logits equal the restatement; the bf16 run completes and stays close
+    for the typical position (a token may take another expert where its best candidates nearly tie)."""
+    rng = random.Random(seed)
+    cfg = _random_config(rng, odd=seed % 2 == 1)
+    w = O.random_model(cfg, seed=seed)
+    lens = [rng.choice([1, 5, 23, 60, 97, 150])] + [rng.choice([30, 90, 130]) for _ in range(rng.randint(1, 3))]
+    toks = [_tokens(cfg, n, seed * 10 + i) for i, n in enumerate(lens)]
+    refs = [O.forward(cfg, w, t) for t in toks]
+    plan, fed = [], [0] * len(lens)
+    while any(f < n for f, n in zip(fed, lens)):
+        step = []
+        for i, n in enumerate(lens):
+            if fed[i] < n and rng.random() < 0.8:
+                left = n - fed[i]
+                c = 1 if left <= 20 else min(left - 20, rng.choice([1, 2, 3, 7, 16, 29, 64, 66, 128]))
+                step.append((i, c))
+                fed[i] += c
+        if step:
+            plan.append(step)
+    pool = -(-sum(lens) // 64) * 64
+    for dtype in (torch.float32, torch.bfloat16):
+        runner = _runner(cfg, w, dtype=dtype, max_tokens=pool)
+        got, reqs, fed = [[] for _ in lens], {}, [0] * len(lens)
+        for step in plan:
+            entries, want, at = [], [], 0
+            for i, c in step:
+                if i not in reqs:
+                    reqs[i] = runner.open_request()
+                entries.append((reqs[i], toks[i][fed[i]:fed[i] + c]))
+                want += list(range(at, at + c))
+                at += c
+            logits = runner.forward_ragged(entries, want).float().cpu()
+            at = 0
+            for i, c in step:
+                got[i].append(logits[at:at + c])
+                at += c
+                fed[i] += c
+                if fed[i] == lens[i]:
+                    runner.close_request(reqs.pop(i))
+        assert runner.kv_cache_manager.can_use_mem_size == pool
+        for i in range(len(lens)):
+            if dtype == torch.float32:
+                _close(torch.cat(got[i]), refs[i], 1e-4)
+            else:
+                d = torch.cat(got[i]).double() - torch.as_tensor(refs[i])
+                rel = (d - d.mean(-1, keepdim=True)).pow(2).mean(-1).sqrt() / max(float(refs[i].std()), 1e-9)
+                assert rel.median().item() < 0.08, rel.median().item()
