@@ -552,7 +552,8 @@ def test_checkpoint_directory_and_greedy_generation_through_the_engine(tmp_path)
     assert runner.kv_cache_manager.can_use_mem_size == 160
 
 
-def test_engine_generates_past_the_pool_size_when_every_layer_has_a_window():
+@pytest.mark.parametrize("graphs", [False, True])
+def test_engine_generates_past_the_pool_size_when_every_layer_has_a_window(graphs):
     """Two requests of 30 + 150 tokens each through a pool of 200 rows: admission counts what the windows keep, the
     runner gives unseen rows back, and the greedy tokens follow the restatement."""
     from lite_llama_b200.engine import Engine
@@ -561,7 +562,7 @@ def test_engine_generates_past_the_pool_size_when_every_layer_has_a_window():
     cfg = O.make_config([O.layer_entry(a, O.moe_entry()), O.layer_entry(a, O.moe_entry(), 0)])
     w = O.random_model(cfg, seed=23, spread=2.0)
     runner = _runner(cfg, w, max_tokens=200, max_requests=2)
-    engine = Engine(runner, max_step_tokens=32, max_portion=8, decode_graphs=False)
+    engine = Engine(runner, max_step_tokens=32, max_portion=8, decode_graphs=graphs)      # replayed decode steps too
     prompts = [_tokens(cfg, 30, 50), _tokens(cfg, 30, 51)]
     outs = engine.generate(prompts, 150)
     assert [len(o) for o in outs] == [150, 150] and runner.kv_cache_manager.can_use_mem_size == 200
