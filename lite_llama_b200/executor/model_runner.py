@@ -346,6 +346,11 @@ class ModelRunner:
             widths = tuple(range(1, self.max_request_num + 1)) if self.max_request_num <= 8 else DEFAULT_BATCH_SIZES
         widths = tuple(w for w in widths if 1 <= w <= min(self.max_request_num, self.kv_cache_manager.max_num_tokens))
         caps = sorted({min(b, self.max_seq_len) for b in ctx_buckets} | {self.max_seq_len})
+        if self.keep_positions:
+            # every cached layer has a window: a token sees at most `window` keys whatever its context, so all buckets
+            # from the longest window up capture the same launches -- one graph (the longest bucket) serves them
+            longest = self.keep_positions + 1 - 64
+            caps = [c for c in caps if c < longest] + [self.max_seq_len]
         try:
             for w in widths:
                 for c in caps:
