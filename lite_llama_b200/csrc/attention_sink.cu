@@ -648,21 +648,49 @@ int launch_attention_split(const AttnArgs& a, int64_t num_seqs, cudaStream_t st)
   return B2L_OK;
 }
 
+// One CTA of 64 threads per (head, sequence): the ranges' maxima and sums are reduced across the threads, every range's
+// weight exp(m_i - m) is computed once into shared memory, then thread d sums its value column over the ranges.
+constexpr int kMergeCached = 256;      // ranges whose weights are kept in shared memory (more: recomputed per column)
+
 template <typename T>
-__global__ void sink_attention_merge_kernel(T* __restrict__ out, int64_t out_stride, const float* __restrict__ part,
-                                            const T* __restrict__ sink, const int* __restrict__ seq_start,
-                                            const int* __restrict__ seq_list, int H, int Dv, int nsplit) {
+__global__ void __launch_bounds__(64) sink_attention_merge_kernel(T* __restrict__ out, int64_t out_stride,
+                                                                  const float* __restrict__ part,
+                                                                  const T* __restrict__ sink,
+                                                                  const int* __restrict__ seq_start,
+                                                                  const int* __restrict__ seq_list, int H, int Dv,
+                                                                  int nsplit) {
   pdl_prologue();
+  __shared__ float wsm[kMergeCached];
+  __shared__ float red[2];
   const int z = blockIdx.y, h = blockIdx.x, s = seq_list ? seq_list[z] : z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* p = part + ((int64_t)z * H + h) * nsplit * (Dv + 2);
-  float mf = sink ? to_f32(sink[h]) : -INFINITY;
-  for (int i = 0; i < nsplit; ++i) mf = fmaxf(mf, p[i * (Dv + 2)]);
-  float den = sink ? expf(to_f32(sink[h]) - mf) : 0.f;
-  for (int i = 0; i < nsplit; ++i) den += p[i * (Dv + 2) + 1] * expf(p[i * (Dv + 2)] - mf);
+  float mf = -INFINITY;
+  for (int i = tid; i < nsplit; i += 64) mf = fmaxf(mf, p[i * (Dv + 2)]);
+  mf = warp_reduce_max(mf);
+  if (lane == 0) red[warp] = mf;
+  __syncthreads();
+  mf = fmaxf(red[0], red[1]);
+  if (sink) mf = fmaxf(mf, to_f32(sink[h]));
+  __syncthreads();
+  float den = 0.f;
+  for (int i = tid; i < nsplit; i += 64) {
+    const float w = expf(p[i * (Dv + 2)] - mf);          // exp(-inf) = 0 for an empty range
+    if (i < kMergeCached) wsm[i] = w;
+    den += p[i * (Dv + 2) + 1] * w;
+  }
+  den = warp_reduce_sum(den);
+  if (lane == 0) red[warp] = den;
+  __syncthreads();
+  den = red[0] + red[1];
+  if (sink) den += expf(to_f32(sink[h]) - mf);
   T* o = out + (int64_t)seq_start[s] * out_stride + h * Dv;
-  for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
+  for (int d = tid; d < Dv; d += 64) {
     float v = 0.f;
-    for (int i = 0; i < nsplit; ++i) v = fmaf(p[i * (Dv + 2) + 2 + d], expf(p[i * (Dv + 2)] - mf), v);
+    for (int i = 0; i < nsplit; ++i) {
+      const float w = i < kMergeCached ? wsm[i] : expf(p[i * (Dv + 2)] - mf);
+      v = fmaf(p[i * (Dv + 2) + 2 + d], w, v);
+    }
     o[d] = from_f32<T>(v / den);
   }
 }
